@@ -1,0 +1,152 @@
+/*
+ * nvllm_b200_attn.h -- C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * One shared library, libnvllm_b200_attn.so, replaces the device work behind
+ * three call sites of nanovllm_jax (paths relative to the reference project):
+ *
+ *   store_kv_to_cache                    layers/attention.py:42-77
+ *   paged_attention (decode)             layers/pallas_attention.py:465-507
+ *                                        -> paged_decode_attention_vectorized :146-238
+ *   variable_length_attention_prefill    layers/attention.py:135-279
+ *   (also reached as paged_prefill_attention, layers/pallas_attention.py:557-608)
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the current CUDA device unless the
+ *     parameter name ends in _host.  The caller owns every buffer.  Unless a
+ *     function's comment says otherwise the library never allocates or frees
+ *     device memory and never synchronises: each call only enqueues work on
+ *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *   - Tensors are dense row-major.  K/V caches, q, k, v and outputs are bf16
+ *     (2 bytes); index tensors are int32.
+ *   - Return value: 0 on success, a negative NVLLM_B200_E* code otherwise.
+ *     Nothing throws or aborts.  nvllm_b200_last_error_string() returns a
+ *     thread-local description of the most recent failure on this thread.
+ *   - Supported set: head_dim == 128; block_size a multiple of 64 (the
+ *     reference asserts a multiple of 256, config.py:38); num_heads a multiple
+ *     of num_kv_heads with ratio <= 8 (decode) / any ratio (prefill); bf16.
+ *     Anything else returns NVLLM_B200_EUNSUPPORTED -- there is no fallback path.
+ *   - Thread safety: re-entrant; calls may come from any host thread; work is
+ *     ordered by the stream it is enqueued on.
+ */
+#ifndef NVLLM_B200_ATTN_H_
+#define NVLLM_B200_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVLLM_B200_OK            0
+#define NVLLM_B200_EINVAL       -1  /* null pointer, negative size, misaligned pointer */
+#define NVLLM_B200_EUNSUPPORTED -2  /* shape outside the supported set */
+#define NVLLM_B200_EWORKSPACE   -3  /* workspace missing or too small */
+#define NVLLM_B200_ECUDA        -4  /* a CUDA runtime call or kernel launch failed */
+#define NVLLM_B200_EDRIVER      -5  /* cuTensorMapEncodeTiled unavailable / failed */
+
+/* Element type of the k/v rows handed to nvllm_b200_store_kvcache. */
+#define NVLLM_B200_DTYPE_BF16 0
+#define NVLLM_B200_DTYPE_F32  1
+
+/* Library version, major*10000 + minor*100 + patch. */
+int nvllm_b200_version(void);
+
+/* Thread-local text for the last non-zero return on this thread ("" if none). */
+const char* nvllm_b200_last_error_string(void);
+
+/*
+ * store_kvcache: k_cache[slot_mapping[t]] = bf16(k[t]), v_cache[...] = bf16(v[t]).
+ * Replaces store_kv_to_cache, layers/attention.py:42-77 (called at :465-467).
+ *
+ *   k, v          [T, KVH, D]            bf16 or f32 (src_dtype); f32 is rounded
+ *                                        to nearest-even, as the reference's
+ *                                        astype(cache dtype) at :70-71
+ *   k_cache, v_cache [num_slots, KVH, D] bf16, updated in place (the reference
+ *                                        donates them, :42)
+ *   slot_mapping  [T] int32              flat slot = block * block_size + offset
+ *
+ * A slot < 0 is SKIPPED, which is what the reference documents (:57-58); the
+ * reference code as written instead overwrites slot 0 (:64-67) -- its model
+ * runner never emits a negative slot (engine/model_runner.py:300-309,361), so
+ * the two never differ in practice.  A slot >= num_slots is dropped (:74-75).
+ * Slots must be unique within a call (the block manager guarantees it).
+ */
+int nvllm_b200_store_kvcache(const void* k, const void* v, void* k_cache, void* v_cache,
+                             const int32_t* slot_mapping, int64_t T, int KVH, int D,
+                             int64_t num_slots, int src_dtype, void* stream);
+
+/*
+ * Bytes of scratch nvllm_b200_paged_decode needs for these sizes (always > 0,
+ * a multiple of 256).  Depends only on (H, D) and the device's SM count.
+ */
+size_t nvllm_b200_paged_decode_workspace_bytes(int B, int H, int KVH, int D, int MB, int block_size);
+
+/*
+ * paged_decode: out[b,h,:] = softmax(scale * q[b,h,:] . K_b^T) V_b over the
+ * first context_lens[b] tokens of the pages block_tables[b,:], kv head = h / (H/KVH).
+ * Replaces paged_attention, layers/pallas_attention.py:465-507 and its live body
+ * paged_decode_attention_vectorized :146-238 (called from layers/attention.py:389-397).
+ *
+ *   q             [B, H, D] bf16
+ *   k_cache, v_cache [NB, block_size, KVH, D] bf16
+ *   block_tables  [B, MB] int32, -1 padded; ids are clamped to [0, NB-1] (:185)
+ *                 and only the first ceil(ctx/block_size) entries of a row are read
+ *   context_lens  [B] int32; clamped to [0, MB*block_size]; 0 gives a zero row
+ *   out           [B, H, D] bf16
+ *   workspace     >= nvllm_b200_paged_decode_workspace_bytes(...) bytes, 256-byte
+ *                 aligned; contents need not be initialised and are not preserved
+ *
+ * Math: fp32 scores and softmax, bf16 probabilities into the P.V product with
+ * fp32 accumulation; 1e-9 is added to the softmax denominator as in :227.
+ * Tokens at positions >= context_lens[b] are never used, whatever bytes their
+ * cache rows hold.
+ */
+int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_cache,
+                            const int32_t* block_tables, const int32_t* context_lens, void* out,
+                            void* workspace, size_t workspace_bytes,
+                            int B, int H, int KVH, int D, int NB, int block_size, int MB,
+                            float scale, void* stream);
+
+/*
+ * Reads (and leaves set) the device-side error flags of the current device into
+ * *flags_host.  0 = no kernel of this library ever gave up a bounded wait.
+ * Bit 0 / 1: paged_decode producer / consumer timed out on a pipeline barrier.
+ * Bit 2 / 3: varlen_prefill pipeline wait timed out / TMEM allocation failed.
+ * This call synchronises with the device (it copies one int back).
+ */
+int nvllm_b200_device_status(int* flags_host);
+
+/* Bytes of scratch nvllm_b200_varlen_prefill needs (may be 0). */
+size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KVH, int D);
+
+/*
+ * varlen_prefill: causal attention over B packed sequences,
+ * out[t,h,:] = softmax_{s <= pos(t)}(scale * q[t,h,:] . k[s,h/(H/KVH),:]) v[s,...].
+ * Replaces variable_length_attention_prefill, layers/attention.py:135-279
+ * (via Attention._prefill_attention :331-364) and paged_prefill_attention,
+ * layers/pallas_attention.py:557-608.
+ *
+ *   q             [T, H, D] bf16;  k, v [T, KVH, D] bf16;  out [T, H, D] bf16
+ *   cu_seqlens_q, cu_seqlens_k  [B+1] int32 DEVICE arrays; they must be equal
+ *                 element-wise (prompt without cached prefix -- the only case in
+ *                 which the reference function is correct); cu_seqlens_host, if
+ *                 not NULL, is a host copy of cu_seqlens_q that lets the library
+ *                 size its grid without reading device memory
+ *   max_seqlen    upper bound of any sequence length (used for grid sizing when
+ *                 cu_seqlens_host is NULL)
+ *
+ * Unlike the reference, rows beyond the 8192-token bucket (utils/context.py:18-32)
+ * are computed rather than returned as zeros.
+ */
+int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v,
+                              const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                              const int32_t* cu_seqlens_host, void* out,
+                              void* workspace, size_t workspace_bytes,
+                              int64_t T, int B, int max_seqlen, int H, int KVH, int D,
+                              float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVLLM_B200_ATTN_H_ */

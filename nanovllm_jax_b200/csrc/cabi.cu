@@ -1,0 +1,46 @@
+// Library-wide host helpers: version, thread-local error text, device queries,
+// and the driver entry point used to encode TMA descriptors.
+#include "common.cuh"
+
+#include <mutex>
+#include <string.h>
+
+namespace nvllm {
+
+char* last_error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+EncodeTiledFn encode_tiled_fn() {
+    static std::once_flag once;
+    static EncodeTiledFn fn = nullptr;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+        (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+}  // namespace nvllm
+
+extern "C" int nvllm_b200_version(void) { return 100; }
+
+extern "C" const char* nvllm_b200_last_error_string(void) { return nvllm::last_error_buffer(); }

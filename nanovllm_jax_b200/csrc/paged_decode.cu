@@ -1,0 +1,571 @@
+// paged_decode: flash-decoding over the block-table KV cache for sm_100a.
+//
+// Replaces paged_attention / paged_decode_attention_vectorized of the
+// reference (layers/pallas_attention.py:465-507, :146-238).
+//
+// The op is HBM-bound: every live K and V row is read exactly once.  Design:
+//
+//  * Work unit = one 64-token tile of one (sequence, kv head).  All tiles of
+//    one kv head are laid end to end (sequence after sequence) and cut into
+//    `num_groups` equal contiguous ranges ("stream-K" partition), so every CTA
+//    streams the same number of bytes no matter how skewed the context lengths
+//    are.  CTA c serves kv head c % KVH of group c / KVH; the KVH CTAs of a
+//    group walk the same tokens at the same pace, so the 256-byte per-head rows
+//    they fetch are neighbours in DRAM.
+//  * Persistent CTAs, 2 per SM: one producer warp issues TMA tile loads
+//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 3-stage
+//    mbarrier ring and runs ahead across sequence boundaries; four consumer
+//    warps each own 16 tokens of a tile.
+//  * The G = H/KVH query heads that share a kv head are packed into the 16-row
+//    M dimension of mma.sync.m16n8k16 (bf16 in, fp32 accumulate) for both
+//    q.K^T and P.V; the online softmax (exp2 domain) lives in registers with
+//    warp-shuffle row reductions.
+//  * A range that ends inside a sequence leaves an fp32 partial (m, l, O) in
+//    the caller's workspace; a second, tiny kernel merges the partials of split
+//    sequences.  Sequences wholly inside one range are written directly.
+//
+// No spin-wait is unbounded: every mbarrier wait gives up after a poll limit,
+// raises a device error flag (readable through nvllm_b200_device_status) and
+// the CTA drains and returns.
+#include "common.cuh"
+
+#include <mutex>
+
+namespace nvllm {
+namespace decode {
+
+constexpr int kTile = 64;                      // tokens per tile
+constexpr int kD = 128;                        // head_dim
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kStages = 3;
+constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
+constexpr int kPanelBytes = kTile * 128;       // 64 tokens x 64 dims bf16, 128B-swizzled
+constexpr int kTileBytes = 2 * kPanelBytes;    // one K or V tile
+constexpr int kQBytes = kMaxG * kD * 2;        // 2 KiB
+constexpr int kStageBytes = 2 * kTileBytes + kQBytes;  // 34816
+constexpr int kOsStride = kD + 8;              // padded row of the cross-warp merge buffers (bank spread)
+constexpr int kOsBytes = 2 * kMaxG * kOsStride * 4;  // two buffers [8][136] fp32
+constexpr int kMiscBytes = 1024;
+constexpr int kSmemBytes = kStages * kStageBytes + kOsBytes + kMiscBytes + 1024;  // + alignment slack
+constexpr int kCtasPerSm = 2;
+
+// Per-partial record in the workspace: O[G][128] fp32, then m[8], l[8].
+__host__ __device__ inline size_t partial_floats(int G) { return (size_t)G * kD + 2 * kMaxG; }
+
+__device__ int g_error_flag = 0;
+
+struct Params {
+    const __nv_bfloat16* q;
+    const int32_t* block_tables;
+    const int32_t* context_lens;
+    __nv_bfloat16* out;
+    float* partials;   // [grid][2][partial_floats]
+    int32_t* prefix;   // [B+1] exclusive prefix of tiles per sequence, last = total
+    int B, H, KVH, G, NB, block_size, MB;
+    int num_groups;
+    float scale_log2;
+};
+
+__device__ __forceinline__ int clamp_ctx(int c, int max_ctx) { return c < 0 ? 0 : (c > max_ctx ? max_ctx : c); }
+__device__ __forceinline__ int tiles_of(int ctx) { return (ctx + kTile - 1) / kTile; }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col); rows 8..15 of A are zero here.
+__device__ __forceinline__ void mma_lo(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t z = 0u;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+
+struct Walk {
+    int b, t;        // current sequence and tile within it
+    long long left;  // tiles still to serve in this CTA's range
+};
+
+// Advance to the next non-empty item; returns tiles in it (0 when done) and its context length.
+__device__ __forceinline__ int next_item(Walk& w, const Params& p, int max_ctx, int& ctx_out, int& tiles_out) {
+    while (w.left > 0 && w.b < p.B) {
+        const int ctx = clamp_ctx(__ldg(p.context_lens + w.b), max_ctx);
+        const int tb = tiles_of(ctx);
+        if (w.t >= tb) {
+            ++w.b;
+            w.t = 0;
+            continue;
+        }
+        long long n = tb - w.t;
+        if (n > w.left) n = w.left;
+        ctx_out = ctx;
+        tiles_out = tb;
+        return (int)n;
+    }
+    return 0;
+}
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* Os = reinterpret_cast<float*>(smem + kStages * kStageBytes);
+    uint8_t* misc = smem + kStages * kStageBytes + kOsBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);            // [kStages]
+    uint64_t* empty_bar = full_bar + kStages;                          // [kStages]
+    int* sm_i = reinterpret_cast<int*>(misc + 64);                     // scan scratch [8] + start [2] + abort [1]
+    volatile int* sm_abort = sm_i + 12;
+    float* sm_ml = reinterpret_cast<float*>(misc + 128);               // [2 parities][m|l][4 warps][8 rows]
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x % p.KVH;
+    const int group = blockIdx.x / p.KVH;
+    const int max_ctx = p.MB * p.block_size;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(empty_bar + s, kConsumerWarps);
+        }
+        fence_mbar_init();
+        sm_i[10] = -1;
+        sm_i[11] = 0;
+        *sm_abort = 0;
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+
+    // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
+    const int per = (p.B + kThreads - 1) / kThreads;
+    const int b_lo = min(p.B, tid * per), b_hi = min(p.B, b_lo + per);
+    int mine = 0;
+    for (int b = b_lo; b < b_hi; ++b) mine += tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) sm_i[warp] = incl;
+    __syncthreads();
+    long long total = 0;
+    int warp_off = 0;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps + 1; ++w) {
+        const int v = sm_i[w];
+        if (w < warp) warp_off += v;
+        total += v;
+    }
+    const long long x0 = group < p.num_groups ? (long long)group * total / p.num_groups : total;
+    const long long x1 = group < p.num_groups ? (long long)(group + 1) * total / p.num_groups : total;
+    {
+        long long run = warp_off + incl - mine;
+        for (int b = b_lo; b < b_hi; ++b) {
+            const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
+            if (blockIdx.x == 0) p.prefix[b] = (int)run;
+            if (tb > 0 && run <= x0 && x0 < run + tb) {
+                sm_i[10] = b;
+                sm_i[11] = (int)(x0 - run);
+            }
+            run += tb;
+        }
+        if (blockIdx.x == 0 && tid == 0) p.prefix[p.B] = (int)total;
+    }
+    __syncthreads();
+    if (x0 >= x1 || sm_i[10] < 0) return;  // nothing to do (uniform across the CTA)
+
+    Walk walk;
+    walk.b = sm_i[10];
+    walk.t = sm_i[11];
+    walk.left = x1 - x0;
+
+    if (warp == kConsumerWarps) {
+        // =========================== producer warp ===========================
+        if (lane == 0) {
+            const uint64_t pol = policy_evict_first();
+            uint32_t it = 0;
+            int ctx, tb, n;
+            bool ok = true;
+            while (ok && (n = next_item(walk, p, max_ctx, ctx, tb)) > 0) {
+                const int32_t* bt = p.block_tables + (size_t)walk.b * p.MB;
+                for (int i = 0; i < n; ++i, ++it) {
+                    const int stage = it % kStages;
+                    const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
+                    if (*sm_abort || !mbar_wait(empty_bar + stage, parity)) {
+                        ok = false;
+                        break;
+                    }
+                    const int tok0 = (walk.t + i) * kTile;
+                    const int bi = tok0 / p.block_size;
+                    int phys = __ldg(bt + bi);
+                    phys = phys < 0 ? 0 : (phys >= p.NB ? p.NB - 1 : phys);
+                    const int slot = phys * p.block_size + (tok0 - bi * p.block_size);
+                    uint8_t* st = smem + stage * kStageBytes;
+                    uint64_t* bar = full_bar + stage;
+                    const uint32_t qbytes = (i == 0) ? (uint32_t)p.G * kD * 2 : 0u;
+                    mbar_expect_tx(bar, 2 * kTileBytes + qbytes);
+                    tma_load_3d_hint(st, &tm_k, bar, 0, kvh, slot, pol);
+                    tma_load_3d_hint(st + kPanelBytes, &tm_k, bar, 64, kvh, slot, pol);
+                    tma_load_3d_hint(st + kTileBytes, &tm_v, bar, 0, kvh, slot, pol);
+                    tma_load_3d_hint(st + kTileBytes + kPanelBytes, &tm_v, bar, 64, kvh, slot, pol);
+                    if (i == 0)
+                        bulk_load(st + 2 * kTileBytes, p.q + ((size_t)walk.b * p.H + (size_t)kvh * p.G) * kD, qbytes,
+                                  bar);
+                }
+                walk.left -= n;
+                walk.t += n;
+            }
+            if (!ok) {
+                *sm_abort = 1;
+                atomicOr(&g_error_flag, 1);
+                // Let loads already issued land before the CTA's shared memory is released.
+                for (uint32_t j = (it >= kStages ? it - kStages : 0); j < it; ++j)
+                    (void)mbar_wait(full_bar + (j % kStages), (j / kStages) & 1u, 1u << 16);
+            }
+        }
+        return;
+    }
+
+    // ============================= consumer warps =============================
+    const int row = lane >> 2;       // query head within the group (valid if < G)
+    const int quad = lane & 3;
+    const int mi = lane >> 3;        // which 8x8 matrix this lane addresses in ldmatrix.x4
+    const int r8 = lane & 7;
+    const int tok_base = warp * 16;
+    const int ctid = tid;            // 0..127 among consumers
+    uint32_t it = 0, item = 0;
+    int ctx, tb, n;
+    bool ok = true;
+
+    for (; ok && (n = next_item(walk, p, max_ctx, ctx, tb)) > 0; ++item) {
+        const bool full_item = (walk.t == 0 && walk.t + n == tb);
+        // (m, l) exchange buffers alternate between consecutive items so that a warp that races ahead
+        // into the next item cannot overwrite values a slower warp is still reading.
+        float* sm_m = sm_ml + (item & 1u) * (2 * kConsumerWarps * kMaxG);
+        float* sm_l = sm_m + kConsumerWarps * kMaxG;
+        uint32_t qa[8][2];
+        float o[16][4];
+        float m = -INFINITY, l = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+        for (int i = 0; i < n; ++i, ++it) {
+            const int stage = it % kStages;
+            if (*sm_abort || !mbar_wait(full_bar + stage, (it / kStages) & 1u)) {
+                ok = false;
+                break;
+            }
+            uint8_t* st = smem + stage * kStageBytes;
+            if (i == 0) {
+                const uint32_t* qs = reinterpret_cast<const uint32_t*>(st + 2 * kTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    qa[ks][0] = row < p.G ? qs[row * 64 + ks * 8 + quad] : 0u;
+                    qa[ks][1] = row < p.G ? qs[row * 64 + ks * 8 + 4 + quad] : 0u;
+                }
+            }
+            const int valid = ctx - ((walk.t + i) * kTile + tok_base);  // live tokens in this warp's 16-token slice
+            if (valid > 0) {
+                const uint32_t kbase = smem_u32(st);
+                const uint32_t vbase = kbase + kTileBytes;
+                if (valid < 16) {
+                    // Rows past the context end may hold anything (even NaN bit patterns): zero the V rows so
+                    // that 0 * garbage cannot reach the accumulators.  Each row is 2 panels x 8 chunks of 16 B.
+                    for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
+                        const int r = tok_base + valid + (idx >> 4);
+                        const int c = idx & 15;
+                        uint8_t* dst = st + kTileBytes + (c >> 3) * kPanelBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();  // order these generic writes before the stage's next TMA refill
+                    __syncwarp();
+                }
+                // ---- S = Q K^T for 16 tokens: two n-tiles of 8 tokens ----
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    const int tok = tok_base + (mi >> 1) * 8 + r8;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const int chunk = ks * 2 + (mi & 1);
+                        const uint32_t addr =
+                            kbase + (chunk >> 3) * kPanelBytes + tok * 128 + (((chunk & 7) ^ r8) << 4);
+                        uint32_t b0, b1, b2, b3;
+                        ldsm_x4(addr, b0, b1, b2, b3);
+                        mma_lo(s0, qa[ks][0], qa[ks][1], b0, b1);
+                        mma_lo(s1, qa[ks][0], qa[ks][1], b2, b3);
+                    }
+                }
+                // ---- online softmax (log2 domain) ----
+                const int c0 = 2 * quad;
+                float v00 = (c0 < valid) ? s0[0] * p.scale_log2 : -INFINITY;
+                float v01 = (c0 + 1 < valid) ? s0[1] * p.scale_log2 : -INFINITY;
+                float v10 = (c0 + 8 < valid) ? s1[0] * p.scale_log2 : -INFINITY;
+                float v11 = (c0 + 9 < valid) ? s1[1] * p.scale_log2 : -INFINITY;
+                float rmax = fmaxf(fmaxf(v00, v01), fmaxf(v10, v11));
+                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+                const float m_new = fmaxf(m, rmax);
+                const float alpha = fast_exp2(m - m_new);
+                v00 = fast_exp2(v00 - m_new);
+                v01 = fast_exp2(v01 - m_new);
+                v10 = fast_exp2(v10 - m_new);
+                v11 = fast_exp2(v11 - m_new);
+                l = l * alpha + ((v00 + v01) + (v10 + v11));
+                m = m_new;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    o[j][0] *= alpha;
+                    o[j][1] *= alpha;
+                }
+                const uint32_t pa0 = pack_bf16(v00, v01), pa2 = pack_bf16(v10, v11);
+                // ---- O += P V: 16 n-tiles of 8 dims, two per ldmatrix.x4.trans ----
+                {
+                    const int tok = tok_base + (mi & 1) * 8 + r8;
+#pragma unroll
+                    for (int np = 0; np < 8; ++np) {
+                        const int chunk = np * 2 + (mi >> 1);
+                        const uint32_t addr =
+                            vbase + (chunk >> 3) * kPanelBytes + tok * 128 + (((chunk & 7) ^ r8) << 4);
+                        uint32_t b0, b1, b2, b3;
+                        ldsm_x4_t(addr, b0, b1, b2, b3);
+                        mma_lo(o[2 * np], pa0, pa2, b0, b1);
+                        mma_lo(o[2 * np + 1], pa0, pa2, b2, b3);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar + stage);
+        }
+        if (!ok) break;
+
+        // ---- merge the four warps' (m, l, O) and emit the item ----
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (quad == 0) {
+            sm_m[warp * kMaxG + row] = m;
+            sm_l[warp * kMaxG + row] = l;
+        }
+        named_barrier_sync(1, kConsumerWarps * 32);
+        {
+            // Fixed-order reduction (bitwise reproducible): warps 0,1 store, warps 2,3 add, readers sum the two.
+            float mt = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) mt = fmaxf(mt, sm_m[w * kMaxG + row]);
+            const float f = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+            float* dst = Os + (warp & 1) * (kMaxG * kOsStride) + row * kOsStride + 2 * quad;
+            if (warp < 2) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][0] * f, o[j][1] * f);
+            }
+            named_barrier_sync(1, kConsumerWarps * 32);
+            if (warp >= 2) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float2 cur = *reinterpret_cast<float2*>(dst + j * 8);
+                    cur.x += o[j][0] * f;
+                    cur.y += o[j][1] * f;
+                    *reinterpret_cast<float2*>(dst + j * 8) = cur;
+                }
+            }
+        }
+        named_barrier_sync(1, kConsumerWarps * 32);
+        {
+            float* part = nullptr;
+            if (!full_item)
+                part = p.partials + ((size_t)blockIdx.x * 2 + (walk.t == 0 ? 1 : 0)) * partial_floats(p.G);
+            for (int r = 0; r < p.G; ++r) {
+                float mt = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) mt = fmaxf(mt, sm_m[w * kMaxG + r]);
+                float lt = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const float mw = sm_m[w * kMaxG + r];
+                    if (mw != -INFINITY) lt += sm_l[w * kMaxG + r] * fast_exp2(mw - mt);
+                }
+                const float acc = Os[r * kOsStride + ctid] + Os[(kMaxG + r) * kOsStride + ctid];
+                if (full_item) {
+                    p.out[((size_t)walk.b * p.H + (size_t)kvh * p.G + r) * kD + ctid] =
+                        __float2bfloat16_rn(acc / (lt + 1e-9f));
+                } else {
+                    part[r * kD + ctid] = acc;
+                    if (ctid == 0) {
+                        part[p.G * kD + r] = mt;
+                        part[p.G * kD + kMaxG + r] = lt;
+                    }
+                }
+            }
+        }
+        walk.left -= n;
+        walk.t += n;
+    }
+    if (!ok) {
+        *sm_abort = 1;
+        atomicOr(&g_error_flag, 2);
+    }
+}
+
+// One CTA per (sequence, kv head): combine the partials of a sequence whose tiles were cut across
+// groups; write zero rows for empty sequences; leave everything else alone.
+__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const Params p, int grid_main) {
+    const int b = blockIdx.x / p.KVH, kvh = blockIdx.x % p.KVH;
+    const int d = threadIdx.x;
+    const long long total = p.prefix[p.B];
+    const long long first = p.prefix[b];
+    const long long tb = p.prefix[b + 1] - first;
+    __nv_bfloat16* orow = p.out + ((size_t)b * p.H + (size_t)kvh * p.G) * kD;
+    if (tb == 0) {
+        for (int r = 0; r < p.G; ++r) orow[r * kD + d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int ng = p.num_groups;
+    long long gf = ((first + 1) * ng - 1) / total;
+    long long gl = ((first + tb) * ng - 1) / total;
+    if (gf > ng - 1) gf = ng - 1;
+    if (gl > ng - 1) gl = ng - 1;
+    if (gf == gl) return;
+    for (int r = 0; r < p.G; ++r) {
+        float mt = -INFINITY;
+        for (long long g = gf; g <= gl; ++g) {
+            if (g * total / ng >= (g + 1) * total / ng) continue;  // empty group
+            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * partial_floats(p.G);
+            mt = fmaxf(mt, part[p.G * kD + r]);
+        }
+        float acc = 0.f, lt = 0.f;
+        for (long long g = gf; g <= gl; ++g) {
+            if (g * total / ng >= (g + 1) * total / ng) continue;
+            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * partial_floats(p.G);
+            const float f = fast_exp2(part[p.G * kD + r] - mt);
+            acc += part[r * kD + d] * f;
+            lt += part[p.G * kD + kMaxG + r] * f;
+        }
+        orow[r * kD + d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
+    }
+    (void)grid_main;
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+static int main_grid() { return kCtasPerSm * sm_count(); }
+
+static size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+static int make_cache_map(CUtensorMap* map, const void* base, int64_t num_slots, int KVH) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)KVH, (cuuint64_t)num_slots};
+    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)KVH * kD * 2};
+    cuuint32_t box[3] = {64, 1, (cuuint32_t)kTile};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NVLLM_B200_OK;
+}
+
+static int ensure_smem_attr() {
+    static std::mutex mu;
+    static bool done[64];
+    int dev = 0;
+    NVLLM_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+        NVLLM_CUDA_OK(cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        done[dev] = true;
+    }
+    return NVLLM_B200_OK;
+}
+
+}  // namespace decode
+}  // namespace nvllm
+
+extern "C" size_t nvllm_b200_paged_decode_workspace_bytes(int B, int H, int KVH, int D, int MB, int block_size) {
+    using namespace nvllm::decode;
+    (void)D;
+    (void)MB;
+    (void)block_size;
+    if (B < 0 || H <= 0 || KVH <= 0 || H % KVH != 0) return 256;
+    const int G = H / KVH;
+    return round256((size_t)(B + 1) * 4) + round256((size_t)main_grid() * 2 * partial_floats(G) * 4) + 256;
+}
+
+extern "C" int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* block_tables, const int32_t* context_lens, void* out,
+                                       void* workspace, size_t workspace_bytes, int B, int H, int KVH, int D, int NB,
+                                       int block_size, int MB, float scale, void* stream) {
+    using namespace nvllm;
+    using namespace nvllm::decode;
+    if (B < 0 || H <= 0 || KVH <= 0 || NB <= 0 || block_size <= 0 || MB <= 0)
+        return fail(NVLLM_B200_EINVAL, "paged_decode: non-positive size (B=%d H=%d KVH=%d NB=%d block=%d MB=%d)", B, H,
+                    KVH, NB, block_size, MB);
+    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: head_dim %d (only 128)", D);
+    if (block_size % kTile != 0)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: block_size %d must be a multiple of %d", block_size, kTile);
+    if (H % KVH != 0 || H / KVH > kMaxG)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: H/KVH = %d/%d must be an integer <= %d", H, KVH, kMaxG);
+    if ((long long)MB * block_size > 0x3fffffffLL || (long long)NB * block_size > 0x7fffffffLL)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: cache or context too large for 32-bit token indices");
+    if (B == 0) return NVLLM_B200_OK;
+    if (!q || !k_cache || !v_cache || !block_tables || !context_lens || !out)
+        return fail(NVLLM_B200_EINVAL, "paged_decode: null pointer");
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+        return fail(NVLLM_B200_EINVAL, "paged_decode: q/k_cache/v_cache/out must be 16-byte aligned");
+    const size_t need = nvllm_b200_paged_decode_workspace_bytes(B, H, KVH, D, MB, block_size);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))
+        return fail(NVLLM_B200_EWORKSPACE, "paged_decode: workspace of %zu bytes (256-byte aligned) required, got %zu",
+                    need, workspace ? workspace_bytes : (size_t)0);
+    const int grid = main_grid();
+    if (KVH > grid) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: KVH %d exceeds the CTA count %d", KVH, grid);
+    int rc = ensure_smem_attr();
+    if (rc) return rc;
+
+    CUtensorMap tm_k, tm_v;
+    const int64_t num_slots = (int64_t)NB * block_size;
+    if ((rc = make_cache_map(&tm_k, k_cache, num_slots, KVH))) return rc;
+    if ((rc = make_cache_map(&tm_v, v_cache, num_slots, KVH))) return rc;
+
+    Params p;
+    p.q = (const __nv_bfloat16*)q;
+    p.block_tables = block_tables;
+    p.context_lens = context_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.prefix = (int32_t*)workspace;
+    p.partials = (float*)((uint8_t*)workspace + round256((size_t)(B + 1) * 4));
+    p.B = B;
+    p.H = H;
+    p.KVH = KVH;
+    p.G = H / KVH;
+    p.NB = NB;
+    p.block_size = block_size;
+    p.MB = MB;
+    p.num_groups = grid / KVH;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    paged_decode_kernel<<<p.num_groups * KVH, kThreads, kSmemBytes, st>>>(tm_k, tm_v, p);
+    NVLLM_CUDA_OK(cudaGetLastError());
+    paged_decode_merge_kernel<<<B * KVH, kD, 0, st>>>(p, grid);
+    NVLLM_CUDA_OK(cudaGetLastError());
+    return NVLLM_B200_OK;
+}
+
+extern "C" int nvllm_b200_device_status(int* flags_host) {
+    using namespace nvllm;
+    if (!flags_host) return fail(NVLLM_B200_EINVAL, "device_status: null pointer");
+    int v = 0;
+    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(&v, decode::g_error_flag, sizeof(int)));
+    *flags_host = v;
+    return NVLLM_B200_OK;
+}
