@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 #include <string.h>
 
 namespace nvllm {
@@ -37,6 +38,14 @@ EncodeTiledFn encode_tiled_fn() {
         (void)cudaGetLastError();
     });
     return fn;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("NVLLM_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 }  // namespace nvllm

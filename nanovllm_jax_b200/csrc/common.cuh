@@ -41,6 +41,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled_fn();
 
+// Programmatic dependent launch between the library's kernels is on unless NVLLM_B200_PDL=0.
+bool pdl_enabled();
+
 // ---------------------------------------------------------------------------
 // device: PTX wrappers
 // ---------------------------------------------------------------------------
@@ -132,6 +135,14 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
+}
+
+// Programmatic dependent launch.  wait: block until the preceding kernel in the stream has completed
+// and its writes are visible (no-op for a normally launched kernel).  launch_dependents: allow the next
+// kernel's CTAs to be scheduled as soon as every CTA of this grid has issued it.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {

@@ -145,6 +145,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         prefetch_tensormap(&tm_v);
     }
 
+    // Programmatic dependent launch: everything above overlapped the tail of the previous kernel in the
+    // stream; nothing below may touch global memory before that kernel's writes are visible.
+    griddep_wait();
+    griddep_launch_dependents();  // lets the merge kernel's launch proceed while this grid streams
+
     // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
     const int per = (p.B + kThreads - 1) / kThreads;
     const int b_lo = min(p.B, tid * per), b_hi = min(p.B, b_lo + per);
@@ -416,17 +421,21 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     }
 }
 
-// One CTA per (sequence, kv head): combine the partials of a sequence whose tiles were cut across
-// groups; write zero rows for empty sequences; leave everything else alone.
-__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const Params p, int grid_main) {
-    const int b = blockIdx.x / p.KVH, kvh = blockIdx.x % p.KVH;
+// One CTA per (sequence, kv head, query head of the group), one thread per output dim: combine the
+// partials of a sequence whose tiles were cut across groups (fixed order, so bitwise reproducible);
+// write a zero row for an empty sequence; leave every other row alone.
+__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const Params p) {
+    griddep_wait();  // partials, prefix and out rows of the main kernel must be complete and visible
+    const int r = blockIdx.x % p.G;
+    const int kvh = (blockIdx.x / p.G) % p.KVH;
+    const int b = blockIdx.x / (p.G * p.KVH);
     const int d = threadIdx.x;
     const long long total = p.prefix[p.B];
     const long long first = p.prefix[b];
     const long long tb = p.prefix[b + 1] - first;
-    __nv_bfloat16* orow = p.out + ((size_t)b * p.H + (size_t)kvh * p.G) * kD;
+    __nv_bfloat16* orow = p.out + ((size_t)b * p.H + (size_t)kvh * p.G + r) * kD;
     if (tb == 0) {
-        for (int r = 0; r < p.G; ++r) orow[r * kD + d] = __float2bfloat16_rn(0.f);
+        orow[d] = __float2bfloat16_rn(0.f);
         return;
     }
     const int ng = p.num_groups;
@@ -435,24 +444,33 @@ __global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const Params p, 
     if (gf > ng - 1) gf = ng - 1;
     if (gl > ng - 1) gl = ng - 1;
     if (gf == gl) return;
-    for (int r = 0; r < p.G; ++r) {
-        float mt = -INFINITY;
-        for (long long g = gf; g <= gl; ++g) {
-            if (g * total / ng >= (g + 1) * total / ng) continue;  // empty group
-            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * partial_floats(p.G);
-            mt = fmaxf(mt, part[p.G * kD + r]);
+    const size_t pf = partial_floats(p.G);
+    float mt = -INFINITY, acc = 0.f, lt = 0.f;
+    for (long long g0 = gf; g0 <= gl; g0 += 4) {
+        float mv[4], lv[4], ov[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long g = g0 + u;
+            const bool live = g <= gl && (g * total / ng < (g + 1) * total / ng);  // skip empty groups
+            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf;
+            mv[u] = live ? part[p.G * kD + r] : -INFINITY;
+            lv[u] = live ? part[p.G * kD + kMaxG + r] : 0.f;
+            ov[u] = live ? part[r * kD + d] : 0.f;
         }
-        float acc = 0.f, lt = 0.f;
-        for (long long g = gf; g <= gl; ++g) {
-            if (g * total / ng >= (g + 1) * total / ng) continue;
-            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * partial_floats(p.G);
-            const float f = fast_exp2(part[p.G * kD + r] - mt);
-            acc += part[r * kD + d] * f;
-            lt += part[p.G * kD + kMaxG + r] * f;
+        const float mnew = fmaxf(fmaxf(mt, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+        if (mnew == -INFINITY) continue;
+        const float sc = (mt == -INFINITY) ? 0.f : fast_exp2(mt - mnew);
+        acc *= sc;
+        lt *= sc;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float f = (mv[u] == -INFINITY) ? 0.f : fast_exp2(mv[u] - mnew);
+            acc += ov[u] * f;
+            lt += lv[u] * f;
         }
-        orow[r * kD + d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
+        mt = mnew;
     }
-    (void)grid_main;
+    orow[d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
 }
 
 // ---------------------------------------------------------------------------
@@ -554,10 +572,21 @@ extern "C" int nvllm_b200_paged_decode(const void* q, const void* k_cache, const
     p.num_groups = grid / KVH;
     p.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    paged_decode_kernel<<<p.num_groups * KVH, kThreads, kSmemBytes, st>>>(tm_k, tm_v, p);
-    NVLLM_CUDA_OK(cudaGetLastError());
-    paged_decode_merge_kernel<<<B * KVH, kD, 0, st>>>(p, grid);
-    NVLLM_CUDA_OK(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.num_groups * KVH));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_kernel, tm_k, tm_v, p));
+    cfg.gridDim = dim3((unsigned)(B * KVH * p.G));
+    cfg.blockDim = dim3(kD);
+    cfg.dynamicSmemBytes = 0;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel, p));
     return NVLLM_B200_OK;
 }
 

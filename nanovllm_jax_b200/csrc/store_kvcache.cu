@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(kStoreThreads)
 store_kvcache_kernel(const SrcT* __restrict__ k, const SrcT* __restrict__ v, __nv_bfloat16* __restrict__ k_cache,
                      __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int64_t total_chunks,
                      int row_chunks, int64_t num_slots) {
+    griddep_wait();  // k, v and slot_mapping may come from the kernel just before this one
+    griddep_launch_dependents();
     const int64_t base = (int64_t)blockIdx.x * (kStoreThreads * kStoreUnroll) + threadIdx.x;
     uint4 kv[kStoreUnroll], vv[kStoreUnroll];
     int64_t dst[kStoreUnroll];
@@ -87,15 +89,23 @@ extern "C" int nvllm_b200_store_kvcache(const void* k, const void* v, void* k_ca
     const int64_t blocks = (total + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "store_kvcache: T too large");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(kStoreThreads);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
     if (src_dtype == NVLLM_B200_DTYPE_BF16) {
-        store_kvcache_kernel<__nv_bfloat16><<<(unsigned)blocks, kStoreThreads, 0, st>>>(
-            (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-            slot_mapping, total, row_chunks, num_slots);
+        NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, store_kvcache_kernel<__nv_bfloat16>, (const __nv_bfloat16*)k,
+                                         (const __nv_bfloat16*)v, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                         slot_mapping, total, row_chunks, num_slots));
     } else {
-        store_kvcache_kernel<float><<<(unsigned)blocks, kStoreThreads, 0, st>>>(
-            (const float*)k, (const float*)v, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, total,
-            row_chunks, num_slots);
+        NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, store_kvcache_kernel<float>, (const float*)k, (const float*)v,
+                                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, total,
+                                         row_chunks, num_slots));
     }
-    NVLLM_CUDA_OK(cudaGetLastError());
     return NVLLM_B200_OK;
 }

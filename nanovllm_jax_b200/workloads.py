@@ -162,16 +162,19 @@ def config1(trial: int = 0) -> DecodeWorkload:
                                 num_blocks=64, ctx_lo=64, ctx_hi=1024, max_blocks=4)
 
 
-def config2(trial: int = 0) -> DecodeWorkload:
-    """Qwen3-8B shapes: 32 q heads / 8 kv heads, batch 64, ctx U[512,8192], pool of 4096 blocks."""
+def config2(trial: int = 0, num_blocks: int = 4096) -> DecodeWorkload:
+    """Qwen3-8B shapes: 32 q heads / 8 kv heads, batch 64, ctx U[512,8192], pool of 4096 blocks.
+
+    ``num_blocks`` shrinks the physical pool (same sequences, same lengths) for profiler captures that
+    must hold little device memory."""
     return make_decode_workload("cfg2-qwen3-8b-b64", seed=2000 + trial, batch=64, num_heads=32, num_kv_heads=8,
-                                num_blocks=4096, ctx_lo=512, ctx_hi=8192, max_blocks=32)
+                                num_blocks=num_blocks, ctx_lo=512, ctx_hi=8192, max_blocks=32)
 
 
-def config3(trial: int = 0) -> DecodeWorkload:
+def config3(trial: int = 0, num_blocks: int = 8192) -> DecodeWorkload:
     """Qwen3-32B shapes: 64 q heads / 8 kv heads, batch 256, ctx log-U[16,32768], pool of 8192 blocks."""
     return make_decode_workload("cfg3-qwen3-32b-b256", seed=3000 + trial, batch=256, num_heads=64, num_kv_heads=8,
-                                num_blocks=8192, ctx_lo=16, ctx_hi=32768, log_uniform=True, max_blocks=128)
+                                num_blocks=num_blocks, ctx_lo=16, ctx_hi=32768, log_uniform=True, max_blocks=128)
 
 
 def config4(trial: int = 0) -> PrefillWorkload:
