@@ -27,7 +27,7 @@ SIGNATURES = {
     "nvllm_b200_paged_decode": (_i32, [_vp] * 7 + [_sz] + [_i32] * 7 + [_f32, _vp]),
     "nvllm_b200_device_status": (_i32, [_c.POINTER(_i32)]),
     "nvllm_b200_varlen_prefill_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),
-    "nvllm_b200_varlen_prefill": (_i32, [_vp] * 9 + [_sz, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "nvllm_b200_varlen_prefill": (_i32, [_vp] * 8 + [_sz, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
 }
 
 _lock = threading.Lock()

@@ -53,3 +53,13 @@ bool pdl_enabled() {
 extern "C" int nvllm_b200_version(void) { return 100; }
 
 extern "C" const char* nvllm_b200_last_error_string(void) { return nvllm::last_error_buffer(); }
+
+extern "C" int nvllm_b200_device_status(int* flags_host) {
+    using namespace nvllm;
+    if (!flags_host) return fail(NVLLM_B200_EINVAL, "device_status: null pointer");
+    int a = 0, b = 0, rc;
+    if ((rc = read_decode_flags(&a))) return rc;
+    if ((rc = read_prefill_flags(&b))) return rc;
+    *flags_host = a | b;
+    return NVLLM_B200_OK;
+}

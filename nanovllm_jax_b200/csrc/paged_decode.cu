@@ -590,11 +590,9 @@ extern "C" int nvllm_b200_paged_decode(const void* q, const void* k_cache, const
     return NVLLM_B200_OK;
 }
 
-extern "C" int nvllm_b200_device_status(int* flags_host) {
-    using namespace nvllm;
-    if (!flags_host) return fail(NVLLM_B200_EINVAL, "device_status: null pointer");
-    int v = 0;
-    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(&v, decode::g_error_flag, sizeof(int)));
-    *flags_host = v;
+namespace nvllm {
+int read_decode_flags(int* out) {
+    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(out, decode::g_error_flag, sizeof(int)));
     return NVLLM_B200_OK;
 }
+}  // namespace nvllm

@@ -1,7 +1,627 @@
+// varlen_prefill: causal attention over packed variable-length sequences on the
+// sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// Replaces variable_length_attention_prefill (reference layers/attention.py:135-279)
+// and paged_prefill_attention (layers/pallas_attention.py:557-608).
+//
+// Work item = 256 consecutive query rows of one sequence for one query head, handled
+// by one CTA as two 128-row Q tiles (A and B) that share every K/V tile they read.
+// A tiny plan kernel turns cu_seqlens into the item list, longest causal span first,
+// so the hardware block scheduler hands out the heavy items before the light ones;
+// the heads of one (sequence, row block) are adjacent in the grid so that the G heads
+// of a kv head find the K/V tiles of their neighbours in L2.
+//
+// Per CTA (12 warps = 3 warpgroups; the first gives registers away with setmaxnreg, the softmax
+// warpgroups take them):
+//   warp 0      TMA producer: Q tiles once, then K and V tiles [128 tokens x 128 dims]
+//               through two-stage mbarrier rings (cp.async.bulk.tensor, 128-byte
+//               swizzle, no multicast).
+//   warp 1      MMA issuer: S = Q K^T (operands in shared memory) and O += P V (P read
+//               from tensor memory, V from shared memory, MN-major), M = N = 128,
+//               K = 16 per instruction; tcgen05.commit signals the mbarriers.  Also
+//               owns the tensor-memory allocation (512 columns: S_A S_B O_A O_B).
+//   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row
+//               reads its S row from tensor memory, keeps the running max / sum,
+//               writes bf16 P back over S, and rescales O only when the max grew by
+//               more than 2^8 (exact: the stale max is carried into the final
+//               normalisation).  Tiles strictly above the diagonal are skipped, the
+//               diagonal tile is masked element-wise.
+// Every mbarrier wait is bounded; on timeout the CTA raises a device error flag,
+// stops issuing work, and still releases its tensor memory before it exits.
 #include "common.cuh"
-extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t, int, int, int, int) { return 0; }
-extern "C" int nvllm_b200_varlen_prefill(const void*, const void*, const void*, const int32_t*, const int32_t*,
-                                         const int32_t*, void*, void*, size_t, int64_t, int, int, int, int, int, float,
-                                         void*) {
-    return nvllm::fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: kernel not built");
+
+#include <mutex>
+
+namespace nvllm {
+namespace prefill {
+
+__device__ int g_error_flag = 0;  // bit 2: pipeline wait timed out; bit 4: sequence too long for the plan kernel
+
+constexpr int kD = 128;
+constexpr int kTileQ = 128;            // rows per Q tile
+constexpr int kBlockQ = 2 * kTileQ;    // rows per work item
+constexpr int kTileKV = 128;
+constexpr int kThreads = 384;            // 3 warpgroups: {TMA, MMA, 2 idle warps} | softmax A | softmax B
+constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 dims bf16, 128B-swizzled
+constexpr int kTileBytes = 2 * kPanelBytes;
+constexpr int kStages = 2;
+constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;  // Q_A Q_B | K ring | V ring
+constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
+constexpr int kMaxLevels = 2048;       // row blocks per sequence the plan kernel can rank
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct Params {
+    const int32_t* cu_seqlens;
+    const int32_t* items;  // [n_items] (seq << 16) | level, heaviest first; items[-1] slot holds the count
+    __nv_bfloat16* out;
+    int B, H, KVH, G;
+    float scale_log2;
+};
+
+// ------------------------------------------------------------------------------------------
+// tcgen05 wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i), columns c..c+31.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,"
+        "%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+// K-major operand tile [128 rows][128 dims] stored as two 64-dim panels; k-step = 16 dims.
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile_addr, int ks) {
+    return make_desc(tile_addr + (ks >> 2) * kPanelBytes + (ks & 3) * 32, 16, 1024);
+}
+// MN-major operand: V tile [128 tokens][128 dims] as two 64-dim panels; N = dims, K = tokens; k-step = 16 tokens.
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile_addr, int ks) {
+    return make_desc(tile_addr + ks * 16 * 128, kPanelBytes, 1024);
+}
+
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);  // B operand MN-major
+
+// ------------------------------------------------------------------------------------------
+// plan kernel: items sorted by row-block index, largest first
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens, int B,
+                                                            int32_t* __restrict__ items_with_count, int capacity) {
+    __shared__ int hist[kMaxLevels];
+    __shared__ int base[kMaxLevels];
+    __shared__ int max_level;
+    griddep_wait();
+    griddep_launch_dependents();
+    for (int i = threadIdx.x; i < kMaxLevels; i += blockDim.x) hist[i] = 0;
+    if (threadIdx.x == 0) max_level = 0;
+    __syncthreads();
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const int len = cu_seqlens[b + 1] - cu_seqlens[b];
+        int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
+        if (n > kMaxLevels) {
+            n = kMaxLevels;
+            atomicOr(&g_error_flag, 16);
+        }
+        for (int l = 0; l < n; ++l) atomicAdd(&hist[l], 1);
+        atomicMax(&max_level, n);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int l = max_level - 1; l >= 0; --l) {
+            base[l] = run;
+            run += hist[l];
+        }
+        items_with_count[0] = run < capacity ? run : capacity;
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const int len = cu_seqlens[b + 1] - cu_seqlens[b];
+        int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
+        if (n > kMaxLevels) n = kMaxLevels;
+        for (int l = 0; l < n; ++l) {
+            const int slot = atomicAdd(&base[l], 1);
+            if (slot < capacity) items_with_count[1 + slot] = (int32_t)(((uint32_t)b << 16) | (uint32_t)l);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// main kernel
+// ------------------------------------------------------------------------------------------
+struct Shared {
+    uint64_t q_full;
+    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], p_full[2], o_full[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool wait_or_abort(Shared* sh, uint64_t* bar, uint32_t parity) {
+    if (sh->abort_flag) return false;
+    if (mbar_wait(bar, parity)) return true;
+    sh->abort_flag = 1;
+    atomicOr(&g_error_flag, 4);
+    return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;                                   // [2][tile]
+    uint8_t* sK = smem + 2 * kTileBytes;                  // [kStages][tile]
+    uint8_t* sV = sK + kStages * kTileBytes;              // [kStages][tile]
+    Shared* sh = reinterpret_cast<Shared*>(smem + kSmemTiles);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        mbar_init(&sh->q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&sh->k_full[s], 1);
+            mbar_init(&sh->k_empty[s], 1);
+            mbar_init(&sh->v_full[s], 1);
+            mbar_init(&sh->v_empty[s], 1);
+        }
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(&sh->s_full[x], 1);
+            mbar_init(&sh->p_full[x], kTileQ);
+            mbar_init(&sh->o_full[x], 1);
+        }
+        sh->abort_flag = 0;
+        sh->tmem_base = 0xFFFFFFFFu;
+        fence_mbar_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc(&sh->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    griddep_wait();  // the plan kernel's item list (and the caller's q/k/v) must be visible from here on
+
+    // ---- which item ----
+    const int n_items = p.items[0];
+    const int pair = blockIdx.x / p.H;
+    const int head = blockIdx.x - pair * p.H;
+    bool active = pair < n_items && tmem != 0xFFFFFFFFu;
+    int seq_start = 0, L = 0, q0 = 0;
+    if (active) {
+        const uint32_t it = (uint32_t)p.items[1 + pair];
+        const int b = (int)(it >> 16);
+        q0 = (int)(it & 0xFFFFu) * kBlockQ;
+        seq_start = p.cu_seqlens[b];
+        L = p.cu_seqlens[b + 1] - seq_start;
+        active = q0 < L;
+    }
+    const int rows = active ? min(kBlockQ, L - q0) : 0;
+    const int n_a = active ? q0 / kTileKV + 1 : 0;                       // KV tiles seen by Q tile A
+    const int n_b = (active && rows > kTileQ) ? q0 / kTileKV + 2 : 0;    // ... by Q tile B (one more: its diagonal)
+    const int n_kv = max(n_a, n_b);
+    const int kvh = head / p.G;
+
+    if (warp == 0) {
+        // =============================== TMA producer ===============================
+        if (lane == 0 && active) {
+            const int tok_q = seq_start + q0;
+            mbar_expect_tx(&sh->q_full, (n_b > 0 ? 2 : 1) * kTileBytes);
+            tma_load_3d(sQ, &tm_q, &sh->q_full, 0, head, tok_q);
+            tma_load_3d(sQ + kPanelBytes, &tm_q, &sh->q_full, 64, head, tok_q);
+            if (n_b > 0) {
+                tma_load_3d(sQ + kTileBytes, &tm_q, &sh->q_full, 0, head, tok_q + kTileQ);
+                tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, head, tok_q + kTileQ);
+            }
+            for (int j = 0; j < n_kv; ++j) {
+                const int st = j % kStages;
+                const uint32_t par = ((j / kStages) & 1u) ^ 1u;
+                const int tok = seq_start + j * kTileKV;
+                if (!wait_or_abort(sh, &sh->k_empty[st], par)) break;
+                mbar_expect_tx(&sh->k_full[st], kTileBytes);
+                tma_load_3d(sK + st * kTileBytes, &tm_k, &sh->k_full[st], 0, kvh, tok);
+                tma_load_3d(sK + st * kTileBytes + kPanelBytes, &tm_k, &sh->k_full[st], 64, kvh, tok);
+                if (!wait_or_abort(sh, &sh->v_empty[st], par)) break;
+                mbar_expect_tx(&sh->v_full[st], kTileBytes);
+                tma_load_3d(sV + st * kTileBytes, &tm_v, &sh->v_full[st], 0, kvh, tok);
+                tma_load_3d(sV + st * kTileBytes + kPanelBytes, &tm_v, &sh->v_full[st], 64, kvh, tok);
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================
+        if (lane == 0 && active) {
+            const uint32_t qa = smem_u32(sQ), qb = smem_u32(sQ + kTileBytes);
+            const uint32_t s_a = tmem, s_b = tmem + 128, o_a = tmem + 256, o_b = tmem + 384;
+            bool ok = wait_or_abort(sh, &sh->q_full, 0) && wait_or_abort(sh, &sh->k_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t k0 = smem_u32(sK);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) mma_ss(s_a, kmajor_desc(qa, ks), kmajor_desc(k0, ks), kIdescQK, ks > 0);
+                tc_commit(&sh->s_full[0]);
+                if (n_b > 0) {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ss(s_b, kmajor_desc(qb, ks), kmajor_desc(k0, ks), kIdescQK, ks > 0);
+                    tc_commit(&sh->s_full[1]);
+                }
+                tc_commit(&sh->k_empty[0]);
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const int st = j % kStages, stn = (j + 1) % kStages;
+                const uint32_t vaddr = smem_u32(sV + st * kTileBytes);
+                const uint32_t kaddr = smem_u32(sK + stn * kTileBytes);
+                if (!(ok = wait_or_abort(sh, &sh->v_full[st], (j / kStages) & 1u))) break;
+                if (j < n_a) {
+                    if (!(ok = wait_or_abort(sh, &sh->p_full[0], j & 1u))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ts(o_a, s_a + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
+                    tc_commit(&sh->o_full[0]);
+                }
+                if (j + 1 < n_a) {
+                    if (!(ok = wait_or_abort(sh, &sh->k_full[stn], ((j + 1) / kStages) & 1u))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ss(s_a, kmajor_desc(qa, ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
+                    tc_commit(&sh->s_full[0]);
+                }
+                if (j < n_b) {
+                    if (!(ok = wait_or_abort(sh, &sh->p_full[1], j & 1u))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ts(o_b, s_b + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
+                    tc_commit(&sh->o_full[1]);
+                }
+                tc_commit(&sh->v_empty[st]);
+                if (j + 1 < n_b) {
+                    if (!(ok = wait_or_abort(sh, &sh->k_full[stn], ((j + 1) / kStages) & 1u))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_ss(s_b, kmajor_desc(qb, ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
+                    tc_commit(&sh->s_full[1]);
+                }
+                if (j + 1 < n_kv) tc_commit(&sh->k_empty[stn]);
+            }
+        }
+    } else if (warp >= 4) {
+        // ============================ softmax warpgroups ============================
+        const int x = (warp - 4) >> 2;              // 0: tile A, 1: tile B
+        const int n_x = x == 0 ? n_a : n_b;
+        const int quarter = warp & 3;               // tensor-memory lane quarter this warp may touch
+        const int row = quarter * 32 + lane;        // row within the Q tile
+        const int q_pos = q0 + x * kTileQ + row;    // position within the sequence
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem + x * 128 + lane_base;
+        const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
+        float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; ok && j < n_x; ++j) {
+            if (!(ok = wait_or_abort(sh, &sh->s_full[x], j & 1u))) break;
+            tc_fence_after();
+            const bool diagonal = (j == n_x - 1);  // key c of this tile is visible to row r iff c <= r
+            // pass 1: row max (tensor-memory reads are cheap; holding all 128 scores would spill registers)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sv[32];
+                tmem_ld32(t_s + c * 32, sv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float v = __uint_as_float(sv[i]);
+                    mx = fmaxf(mx, (diagonal && c * 32 + i > row) ? -INFINITY : v);
+                }
+            }
+            m_run = fmaxf(m_run, mx);
+            if (j == 0) {
+                m_used = m_run;
+            } else {
+                const bool grow = (m_run - m_used) * p.scale_log2 > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O holds sums relative to m_used: bring it to m_run before more is added.
+                    if (!(ok = wait_or_abort(sh, &sh->o_full[x], (j - 1) & 1u))) break;
+                    tc_fence_after();
+                    const float f = fast_exp2((m_used - m_run) * p.scale_log2);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t ov[32];
+                        tmem_ld32(t_o + c * 32, ov);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                        tmem_st32(t_o + c * 32, ov);
+                    }
+                    tmem_wait_st();
+                    l *= f;
+                    m_used = m_run;
+                }
+            }
+            // pass 2: p = 2^(s*scale - m), packed to bf16 pairs and written over the S columns already consumed
+            // (packed column 16c+i replaces scores 32c+2i, 32c+2i+1: always behind the read position).
+            const float neg = -m_used * p.scale_log2;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t sa[32], sb[32], pk[32];
+                tmem_ld32(t_s + half * 64, sa);
+                tmem_ld32(t_s + half * 64 + 32, sb);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c0 = half * 64 + 2 * i, c1 = half * 64 + 32 + 2 * i;
+                    float a0 = fast_exp2(fmaf(__uint_as_float(sa[2 * i]), p.scale_log2, neg));
+                    float a1 = fast_exp2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale_log2, neg));
+                    float b0 = fast_exp2(fmaf(__uint_as_float(sb[2 * i]), p.scale_log2, neg));
+                    float b1 = fast_exp2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale_log2, neg));
+                    if (diagonal) {
+                        a0 = c0 > row ? 0.f : a0;
+                        a1 = c0 + 1 > row ? 0.f : a1;
+                        b0 = c1 > row ? 0.f : b0;
+                        b1 = c1 + 1 > row ? 0.f : b1;
+                    }
+                    sum0 += a0 + b0;
+                    sum1 += a1 + b1;
+                    pk[i] = pack_bf16(a0, a1);
+                    pk[16 + i] = pack_bf16(b0, b1);
+                }
+                tmem_st32(t_s + half * 32, pk);
+            }
+            l += sum0 + sum1;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->p_full[x]);
+        }
+        // ---- epilogue: O / l -> bf16 -> global ----
+        if (ok && n_x > 0) {
+            ok = wait_or_abort(sh, &sh->o_full[x], (n_x - 1) & 1u);
+            if (ok) {
+                tc_fence_after();
+                const float inv = 1.0f / l;
+                __nv_bfloat16* orow = p.out + ((size_t)(seq_start + q_pos) * p.H + head) * kD;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t ov[32];
+                    tmem_ld32(t_o + c * 32, ov);
+                    tmem_wait_ld();
+                    if (q_pos < L) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 w;
+                            w.x = pack_bf16(__uint_as_float(ov[8 * i + 0]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                            w.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                            w.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                            w.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone meets here, then the allocating warp frees tensor memory ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1 && tmem != 0xFFFFFFFFu) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host
+// ------------------------------------------------------------------------------------------
+static int make_map(CUtensorMap* map, const void* base, int heads, int64_t tokens) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2};
+    cuuint32_t box[3] = {64, 1, 128};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NVLLM_B200_OK;
+}
+
+static int ensure_attr() {
+    static std::mutex mu;
+    static bool done[64];
+    int dev = 0;
+    NVLLM_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+        NVLLM_CUDA_OK(
+            cudaFuncSetAttribute(varlen_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        done[dev] = true;
+    }
+    return NVLLM_B200_OK;
+}
+
+static int64_t item_capacity(int64_t T, int B) { return T / kBlockQ + B + 1; }
+
+}  // namespace prefill
+
+int read_prefill_flags(int* out) {
+    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(out, prefill::g_error_flag, sizeof(int)));
+    return NVLLM_B200_OK;
+}
+namespace prefill {
+
+}  // namespace prefill
+}  // namespace nvllm
+
+extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KVH, int D) {
+    (void)H;
+    (void)KVH;
+    (void)D;
+    if (T < 0 || B < 0) return 256;
+    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 4;
+    return (n + 255) & ~size_t(255);
+}
+
+extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                                         const int32_t* cu_seqlens_k, const int32_t* cu_seqlens_host, void* out,
+                                         void* workspace, size_t workspace_bytes, int64_t T, int B, int max_seqlen,
+                                         int H, int KVH, int D, float scale, void* stream) {
+    using namespace nvllm;
+    using namespace nvllm::prefill;
+    if (T < 0 || B < 0 || H <= 0 || KVH <= 0)
+        return fail(NVLLM_B200_EINVAL, "varlen_prefill: bad size (T=%lld B=%d H=%d KVH=%d)", (long long)T, B, H, KVH);
+    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: head_dim %d (only 128)", D);
+    if (H % KVH != 0) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: H %d not a multiple of KVH %d", H, KVH);
+    if (B > 65535) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: more than 65535 sequences");
+    if (T > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: more than 2^31-1 tokens");
+    if (!(scale > 0.f)) return fail(NVLLM_B200_EINVAL, "varlen_prefill: scale must be positive");
+    if (T == 0 || B == 0) return NVLLM_B200_OK;
+    if (!q || !k || !v || !cu_seqlens_q || !cu_seqlens_k || !out)
+        return fail(NVLLM_B200_EINVAL, "varlen_prefill: null pointer");
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
+        return fail(NVLLM_B200_EINVAL, "varlen_prefill: q/k/v/out must be 16-byte aligned");
+    const size_t need = nvllm_b200_varlen_prefill_workspace_bytes(T, B, H, KVH, D);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))
+        return fail(NVLLM_B200_EWORKSPACE, "varlen_prefill: workspace of %zu bytes required, got %zu", need,
+                    workspace ? workspace_bytes : (size_t)0);
+
+    // Upper bound of (sequence, 256-row block) pairs: exact from the host copy of cu_seqlens, else from max_seqlen.
+    int64_t pairs = 0;
+    const int64_t cap = item_capacity(T, B);
+    if (cu_seqlens_host) {
+        for (int b = 0; b < B; ++b) {
+            const int64_t len = (int64_t)cu_seqlens_host[b + 1] - cu_seqlens_host[b];
+            if (len < 0 || cu_seqlens_host[b + 1] > T)
+                return fail(NVLLM_B200_EINVAL, "varlen_prefill: cu_seqlens_host is not a non-decreasing prefix of T");
+            if (len > (int64_t)kMaxLevels * kBlockQ)
+                return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: sequence of %lld tokens (max %d)", (long long)len,
+                            kMaxLevels * kBlockQ);
+            pairs += (len + kBlockQ - 1) / kBlockQ;
+        }
+    } else {
+        if (max_seqlen <= 0) return fail(NVLLM_B200_EINVAL, "varlen_prefill: max_seqlen must be positive");
+        if (max_seqlen > kMaxLevels * kBlockQ)
+            return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: max_seqlen %d (max %d)", max_seqlen,
+                        kMaxLevels * kBlockQ);
+        pairs = (int64_t)B * ((max_seqlen + kBlockQ - 1) / kBlockQ);
+    }
+    if (pairs > cap) pairs = cap;
+    if (pairs == 0) return NVLLM_B200_OK;
+    if (pairs * H > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: grid too large");
+
+    int rc = ensure_attr();
+    if (rc) return rc;
+    CUtensorMap tm_q, tm_k, tm_v;
+    if ((rc = make_map(&tm_q, q, H, T))) return rc;
+    if ((rc = make_map(&tm_k, k, KVH, T))) return rc;
+    if ((rc = make_map(&tm_v, v, KVH, T))) return rc;
+
+    Params p;
+    p.cu_seqlens = cu_seqlens_q;
+    p.items = (const int32_t*)workspace;
+    p.out = (__nv_bfloat16*)out;
+    p.B = B;
+    p.H = H;
+    p.KVH = KVH;
+    p.G = H / KVH;
+    p.scale_log2 = scale * 1.4426950408889634f;
+
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, B, (int32_t*)workspace, (int)cap));
+    cfg.gridDim = dim3((unsigned)(pairs * H));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, varlen_prefill_kernel, tm_q, tm_k, tm_v, p));
+    return NVLLM_B200_OK;
 }
