@@ -109,6 +109,37 @@ int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_ca
                             float scale, void* stream);
 
 /*
+ * paged_decode_static: the same computation as nvllm_b200_paged_decode, for callers that can give the
+ * library no scratch buffer and cannot allocate one themselves.  It has no counterpart in the reference.
+ *
+ * Who needs it: a host whose operand list is fixed (it can pass inputs and outputs, nothing else) and that
+ * runs where device allocation is off limits at call time -- typically a framework custom-call handler
+ * in a process whose memory pool already owns almost all of HBM, so that a cudaMalloc may fail or take
+ * memory the pool counts on, or a latency-critical loop that must avoid the device-wide synchronisation
+ * cudaMalloc and cudaFree cause.  This entry point calls no allocating routine: its split-K scratch is a
+ * fixed array of about 2.7 MB inside the library image, present on every device that loads the library
+ * for as long as the process lives.
+ *
+ * Limits (beyond those of nvllm_b200_paged_decode): B <= 4096 sequences, and a device with at most
+ * 160 SMs (the main kernel runs 2 CTAs per SM and the array holds the partial results of 320).  Larger
+ * sizes return NVLLM_B200_EWORKSPACE and the error text names the limit; nothing is launched.
+ *
+ * The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
+ * device current, which may also make the runtime load the library's device code); make that first call
+ * outside any stream capture.  Later calls only enqueue kernels on `stream`.
+ *
+ * All calls on a device share the one array, and it keeps whatever the previous call left in it.  Nothing
+ * in it needs to be zero at the start of a call (every word a call reads it has written earlier in the
+ * same call), so there is nothing to clear between calls; but two calls whose kernels may overlap on the
+ * GPU -- different streams, or different host threads without ordering -- race on it and corrupt each
+ * other's results.  Issue them on one stream, or order them with events.
+ */
+int nvllm_b200_paged_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                                   const int32_t* block_tables, const int32_t* context_lens, void* out,
+                                   int B, int H, int KVH, int D, int NB, int block_size, int MB,
+                                   float scale, void* stream);
+
+/*
  * Reads (and leaves set) the device-side error flags of the current device into
  * *flags_host.  0 = no kernel of this library ever gave up a bounded wait.
  * Bit 0 / 1: paged_decode producer / consumer timed out on a pipeline barrier.

@@ -596,3 +596,132 @@ int read_decode_flags(int* out) {
     return NVLLM_B200_OK;
 }
 }  // namespace nvllm
+
+// ---------------------------------------------------------------------------
+// paged decode without a caller-provided workspace
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot hand it scratch memory and cannot obtain any at call time: a custom-call
+// handler whose operand list is fixed by the framework, running in a process where the framework's own pool
+// has already reserved nearly all of HBM (so a cudaMalloc there fails or starves the pool), or a serving
+// loop that must not take the device-wide synchronisation that cudaMalloc / cudaFree imply.  For them the
+// split-K scratch of the decode kernels lives in this fixed array, which every device that loads the
+// library carries until the process exits.
+//
+// Sizes are capped so the array stays small: batch <= kStaticMaxBatch and a main grid of at most
+// kStaticMaxCtas CTAs (2 per SM, i.e. devices with up to 160 SMs).
+namespace nvllm {
+namespace decode {
+
+constexpr int kStaticMaxBatch = 4096;
+constexpr int kStaticMaxCtas = 320;
+constexpr size_t kStaticPrefixBytes = ((size_t)(kStaticMaxBatch + 1) * 4 + 255) & ~size_t(255);
+constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxCtas * 2 * ((size_t)kMaxG * kD + 2 * kMaxG) * 4;
+constexpr size_t kStaticScratchBytes = kStaticPrefixBytes + kStaticPartialBytes;  // about 2.7 MB
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only a handle
+// for the runtime, never a pointer a kernel may use, so the address is looked up once per device (with that
+// device current) and cached.
+static int static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64];
+    int dev = 0;
+    NVLLM_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(NVLLM_B200_ECUDA, "paged_decode_static: cudaGetSymbolAddress failed: %s",
+                        cudaGetErrorString(e));
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return NVLLM_B200_OK;
+}
+
+}  // namespace decode
+}  // namespace nvllm
+
+extern "C" int nvllm_b200_paged_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                                              const int32_t* block_tables, const int32_t* context_lens, void* out,
+                                              int B, int H, int KVH, int D, int NB, int block_size, int MB,
+                                              float scale, void* stream) {
+    using namespace nvllm;
+    using namespace nvllm::decode;
+    if (B < 0 || H <= 0 || KVH <= 0 || NB <= 0 || block_size <= 0 || MB <= 0)
+        return fail(NVLLM_B200_EINVAL, "paged_decode_static: non-positive size (B=%d H=%d KVH=%d NB=%d block=%d MB=%d)",
+                    B, H, KVH, NB, block_size, MB);
+    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: head_dim %d (only 128)", D);
+    if (block_size % kTile != 0)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: block_size %d must be a multiple of %d", block_size,
+                    kTile);
+    if (H % KVH != 0 || H / KVH > kMaxG)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: H/KVH = %d/%d must be an integer <= %d", H, KVH,
+                    kMaxG);
+    if ((long long)MB * block_size > 0x3fffffffLL || (long long)NB * block_size > 0x7fffffffLL)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: cache or context too large for 32-bit token indices");
+    if (B > kStaticMaxBatch)
+        return fail(NVLLM_B200_EWORKSPACE,
+                    "paged_decode_static: batch %d exceeds the built-in scratch (max %d sequences); use "
+                    "nvllm_b200_paged_decode with a caller workspace",
+                    B, kStaticMaxBatch);
+    const int grid = main_grid();
+    if (grid > kStaticMaxCtas)
+        return fail(NVLLM_B200_EWORKSPACE,
+                    "paged_decode_static: this device needs %d CTAs, the built-in scratch holds %d; use "
+                    "nvllm_b200_paged_decode with a caller workspace",
+                    grid, kStaticMaxCtas);
+    if (B == 0) return NVLLM_B200_OK;
+    if (!q || !k_cache || !v_cache || !block_tables || !context_lens || !out)
+        return fail(NVLLM_B200_EINVAL, "paged_decode_static: null pointer");
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+        return fail(NVLLM_B200_EINVAL, "paged_decode_static: q/k_cache/v_cache/out must be 16-byte aligned");
+    if (KVH > grid)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: KVH %d exceeds the CTA count %d", KVH, grid);
+    int rc = ensure_smem_attr();
+    if (rc) return rc;
+    void* scratch = nullptr;
+    if ((rc = static_scratch_address(&scratch))) return rc;
+
+    CUtensorMap tm_k, tm_v;
+    const int64_t num_slots = (int64_t)NB * block_size;
+    if ((rc = make_cache_map(&tm_k, k_cache, num_slots, KVH))) return rc;
+    if ((rc = make_cache_map(&tm_v, v_cache, num_slots, KVH))) return rc;
+
+    Params p;
+    p.q = (const __nv_bfloat16*)q;
+    p.block_tables = block_tables;
+    p.context_lens = context_lens;
+    p.out = (__nv_bfloat16*)out;
+    p.prefix = (int32_t*)scratch;
+    p.partials = (float*)((uint8_t*)scratch + kStaticPrefixBytes);
+    p.B = B;
+    p.H = H;
+    p.KVH = KVH;
+    p.G = H / KVH;
+    p.NB = NB;
+    p.block_size = block_size;
+    p.MB = MB;
+    p.num_groups = grid / KVH;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.num_groups * KVH));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_kernel, tm_k, tm_v, p));
+    cfg.gridDim = dim3((unsigned)(B * KVH * p.G));
+    cfg.blockDim = dim3(kD);
+    cfg.dynamicSmemBytes = 0;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel, p));
+    return NVLLM_B200_OK;
+}
