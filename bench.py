@@ -2,7 +2,7 @@
 """Benchmark of the paged-attention decode step (store_kvcache + paged decode) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload cfg2|cfg3|cfg1] [--scaling weak|strong]
+                    [--workload cfg2|cfg3|cfg1|cfg4] [--scaling weak|strong]
 
 One step = one decode-attention pass over one batch: the step's new K/V rows are scattered into the
 paged cache by slot and every sequence attends over its pages -- what ``Attention.__call__`` does for
@@ -16,6 +16,9 @@ pinned host memory and the result copied back to the host inside the timed regio
 device-resident state, not a step input, exactly as in the reference engine).  ``roofline`` times the
 decode kernels alone with CUDA events inside the timed loop.  ``cpu_baseline`` is the reference's own
 algorithm restated for the host cores (``oracle/``), timed on a bounded sample.
+
+``--workload cfg4`` switches to the prefill step (store_kvcache of all prompt tokens + varlen causal attention,
+16 packed Qwen3-8B sequences) and reports TFLOP/s against the bf16 tensor roofline.
 
 ``--impl reference`` times that CPU restatement alone, on rank 0, each step a bounded sample of the
 same workload.
@@ -437,13 +440,201 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------
+# prefill workload (cfg4): metric = causal attention TFLOP/s, tensor-core roofline
+# ----------------------------------------------------------------------------------------------
+PREFILL_METRIC, PREFILL_UNIT = "varlen_prefill_tflops", "TFLOP/s"
+
+
+def prefill_cpu_sample(w, budget_s: float):
+    """Times the torch-CPU restatement of the reference prefill on the shortest sequences that fit the budget."""
+    import torch
+    from oracle import reference_attention_torch as reft
+    order = np.argsort(w.seq_lens)
+    gen = torch.Generator()
+    gen.manual_seed(w.seed)
+    used, flops, t_total = [], 0, 0.0
+    for b in order:
+        n = int(w.seq_lens[b])
+        est = 4 * w.head_dim * w.num_heads * n * (n + 1) // 2
+        q = torch.randn((n, w.num_heads, w.head_dim), generator=gen).bfloat16()
+        k = torch.randn((n, w.num_kv_heads, w.head_dim), generator=gen).bfloat16()
+        v = torch.randn((n, w.num_kv_heads, w.head_dim), generator=gen).bfloat16()
+        t0 = time.perf_counter()
+        reft.variable_length_attention_prefill(q, k, v, [0, n], w.num_heads, w.num_kv_heads, w.scale)
+        dt = time.perf_counter() - t0
+        used.append(n)
+        flops += est
+        t_total += dt
+        if t_total > budget_s:
+            break
+    return flops / t_total / 1e12, used, t_total, torch.get_num_threads()
+
+
+def prefill_config(w, world, h, kvh):
+    return {"workload": f"{w.name}: varlen causal prefill attention, {w.num_heads} q heads / {w.num_kv_heads} kv heads, "
+                        f"head_dim {w.head_dim}, {w.batch} packed sequences of {int(w.seq_lens.min())}.."
+                        f"{int(w.seq_lens.max())} tokens (T = {w.total_tokens}), plus store_kvcache of all T tokens "
+                        f"(block {w.block_size})",
+            "kv_heads_per_gpu": kvh, "q_heads_per_gpu": h,
+            "parallelism": f"kv-head shards x{world}, no collective in the path",
+            "l2": f"q/k/v/out of one step are {(2 * h + 2 * kvh) * w.total_tokens * w.head_dim * 2 / 1e6:.0f} MB "
+                  f"> 126 MB L2; K/V tile reuse inside a step is meant to hit L2",
+            "seed": w.seed}
+
+
+def run_prefill(args):
+    import torch
+    import torch.distributed as dist
+    from nanovllm_jax_b200 import _lib, ops, workloads
+    from nanovllm_jax_b200.layers.attention import Attention
+    from nanovllm_jax_b200.utils.context import create_prefill_context
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    w = workloads.config4()
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        budget = min(20.0, 150.0 / max(args.steps + args.warmup, 1))
+        vals = [prefill_cpu_sample(w, budget) for _ in range(min(args.steps + args.warmup, 3))]
+        tf, used, dt, threads = vals[-1]
+        sample = f"restated reference prefill (torch CPU, fp32) on the {len(used)} shortest sequences ({used} tokens)"
+        print(json.dumps({"impl": "reference", "metric": PREFILL_METRIC, "value": tf, "unit": PREFILL_UNIT,
+                          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+                          "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic", "config": prefill_config(w, 1, w.num_heads, w.num_kv_heads),
+                          "cpu_baseline": {"value": tf, "unit": PREFILL_UNIT, "cores": threads, "kind": "port",
+                                           "sample": sample},
+                          "e2e": {"value": tf, "unit": PREFILL_UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}), flush=True)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    g = w.num_heads // w.num_kv_heads
+    kvh = w.num_kv_heads // world if args.scaling == "strong" else w.num_kv_heads
+    h = kvh * g
+    t = w.total_tokens
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(w.seed * 100 + rank)
+    q = torch.empty((t, h, w.head_dim), dtype=torch.bfloat16, device=dev)
+    k = torch.empty((t, kvh, w.head_dim), dtype=torch.bfloat16, device=dev)
+    v = torch.empty_like(k)
+    for x in (q, k, v):
+        fill_normal_bf16(x, gen)
+    kc = torch.zeros((w.num_blocks, w.block_size, kvh, w.head_dim), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    attn = Attention(h, w.head_dim, w.scale, kvh, w.block_size)
+    attn.set_kv_cache(kc, vc)
+    cu = torch.from_numpy(w.cu_seqlens).to(dev)
+    slots = torch.from_numpy(w.slot_mapping).to(dev)
+    ctx = create_prefill_context(cu, cu, int(w.seq_lens.max()), int(w.seq_lens.max()), slots,
+                                 cu_seqlens_host=w.cu_seqlens)
+    out = torch.empty_like(q)
+    flat = (w.num_blocks * w.block_size, kvh, w.head_dim)
+    flops = w.flops(h)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        attn(q, k, v, ctx)
+    barrier()
+    ev_every = 4
+    n_ev = (args.steps + ev_every - 1) // ev_every
+    ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(n_ev)]
+    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(n_ev)]
+    t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        t0e.record()
+        for i in range(args.steps):
+            ops.store_kvcache(k, v, kc.view(flat), vc.view(flat), slots)
+            if i % ev_every == 0:
+                ev_a[i // ev_every].record()
+            ops.varlen_prefill(q, k, v, cu, int(w.seq_lens.max()), w.scale, out=out, cu_seqlens_host=w.cu_seqlens)
+            if i % ev_every == 0:
+                ev_b[i // ev_every].record()
+        t1e.record()
+        torch.cuda.synchronize()
+    elapsed_ms = t0e.elapsed_time(t1e)
+    kern_ms = float(np.mean([a.elapsed_time(b) for a, b in zip(ev_a, ev_b)]))
+    if world > 1:
+        tt = torch.tensor([elapsed_ms, kern_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms, kern_ms = float(tt[0]), float(tt[1])
+    barrier()
+    status = _lib.device_status()
+
+    hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+    hout = torch.empty_like(hq).pin_memory()
+    e2e_steps = max(1, min(args.steps, 10))
+
+    def e2e_step():
+        q.copy_(hq, non_blocking=True)
+        k.copy_(hk, non_blocking=True)
+        v.copy_(hv, non_blocking=True)
+        o = attn(q, k, v, ctx)
+        hout.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    tw = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - tw) / e2e_steps * 1e3
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt[0])
+    barrier()
+    if rank == 0:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak, kind = float(json.load(f)["bf16_tflops_sustained"]), "measured sustained cuBLAS bf16"
+        except Exception:
+            peak, kind = 1400.0, "fallback sustained"
+        ms = elapsed_ms / args.steps
+        achieved = flops / (kern_ms / 1e3) / 1e12
+        line = {"metric": PREFILL_METRIC, "value": world * flops / (ms / 1e3) / 1e12, "unit": PREFILL_UNIT,
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": prefill_config(w, world, h, kvh),
+                "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                             "frac": achieved / peak, "traffic": None,
+                             "kernel": "prefill_plan_kernel + varlen_prefill_kernel (one C-ABI call)",
+                             "flops_per_launch": flops, "us_per_launch": kern_ms * 1e3, "peak_kind": kind},
+                "e2e": {"value": world * flops / (e2e_ms / 1e3) / 1e12, "unit": PREFILL_UNIT,
+                        "h2d_bytes_per_step": sum(x.numel() * 2 for x in (hq, hk, hv)),
+                        "d2h_bytes_per_step": hout.numel() * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                        "what": "Attention.__call__ (store_kvcache + varlen prefill) with q/k/v copied from pinned host "
+                                "memory and the output copied back every step"},
+                "clocks": clocks.summary(), "gpu_launches": 3 * args.steps, "device_status": status}
+        if world == 1 and not args.no_cpu_baseline:
+            tf, used, dt, threads = prefill_cpu_sample(w, 12.0)
+            line["cpu_baseline"] = {"value": tf, "unit": PREFILL_UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"restated reference prefill (torch CPU, fp32) on the {len(used)} shortest "
+                                              f"sequences ({used} tokens), {dt:.1f} s; JAX itself is not installed"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=["cfg1", "cfg2", "cfg3"], default="cfg2")
+    ap.add_argument("--workload", choices=["cfg1", "cfg2", "cfg3", "cfg4"], default="cfg2")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--pool-blocks", type=int, default=0,
@@ -452,11 +643,15 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
-        return run_reference(args)
+        return run_prefill(args) if args.workload == "cfg4" else run_reference(args)
     if args.gpus > 1 and "RANK" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__)] + sys.argv[1:]
         os.execv(sys.executable, cmd)
+    if args.workload == "cfg4":
+        if args.steps == 1000:
+            args.steps = 100  # default sized for the decode step; a prefill step is ~10x longer
+        return run_prefill(args)
     run_b200(args)
 
 
