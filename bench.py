@@ -41,9 +41,10 @@ if ROOT not in sys.path:
 METRIC = "paged_decode_attn_hbm_gbps"
 UNIT = "GB/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one paged_decode_kernel launch, from the ncu capture
-# summarised in profiles/ (file named per workload); None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
+# summarised in profiles/paged_decode_cfg2_qwen3-8b_b64.md and profiles/varlen_prefill_cfg4_qwen3-8b_16seq.md
+# (a property of the launch, independent of the page-pool size the capture used); None where no capture exists.
+NCU_TRAFFIC_BYTES = {"cfg2": 1_021_617_440, "cfg4": 1_645_496_488}
 
 
 def load_peaks():
@@ -609,7 +610,7 @@ def run_prefill(args):
                 "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic", "config": prefill_config(w, world, h, kvh),
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                             "frac": achieved / peak, "traffic": None,
+                             "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get("cfg4"),
                              "kernel": "prefill_plan_kernel + varlen_prefill_kernel (one C-ABI call)",
                              "flops_per_launch": flops, "us_per_launch": kern_ms * 1e3, "peak_kind": kind},
                 "e2e": {"value": world * flops / (e2e_ms / 1e3) / 1e12, "unit": PREFILL_UNIT,
