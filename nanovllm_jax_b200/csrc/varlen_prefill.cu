@@ -5,11 +5,13 @@
 // and paged_prefill_attention (layers/pallas_attention.py:557-608).
 //
 // Work item = 256 consecutive query rows of one sequence for one query head, handled
-// by one CTA as two 128-row Q tiles (A and B) that share every K/V tile they read.
-// A tiny plan kernel turns cu_seqlens into the item list, longest causal span first,
-// so the hardware block scheduler hands out the heavy items before the light ones;
-// the heads of one (sequence, row block) are adjacent in the grid so that the G heads
-// of a kv head find the K/V tiles of their neighbours in L2.
+// as two 128-row Q tiles (A and B) that share every K/V tile they read.  A tiny plan
+// kernel turns cu_seqlens into the item list, longest causal span first; one
+// persistent CTA per SM takes items round-robin from that list (heavy ones first, so
+// the CTAs finish together), and the heads of one (sequence, row block) are
+// neighbours in the list so that the G heads of a kv head find each other's K/V
+// tiles in L2.  Tensor memory and barriers are set up once per CTA; the loads of the
+// next item are already in flight while the current one drains.
 //
 // Per CTA (12 warps = 3 warpgroups; the first gives registers away with setmaxnreg, the softmax
 // warpgroups take them):
@@ -21,11 +23,14 @@
 //               K = 16 per instruction; tcgen05.commit signals the mbarriers.  Also
 //               owns the tensor-memory allocation (512 columns: S_A S_B O_A O_B).
 //   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row
-//               reads its S row from tensor memory, keeps the running max / sum,
-//               writes bf16 P back over S, and rescales O only when the max grew by
-//               more than 2^8 (exact: the stale max is carried into the final
-//               normalisation).  Tiles strictly above the diagonal are skipped, the
-//               diagonal tile is masked element-wise.
+//               reads its S row from tensor memory (32-column chunks, the next chunk
+//               in flight while the current one is processed), keeps the running
+//               max / sum, writes bf16 P back over S in two halves -- the first half
+//               releases the first four P.V k-steps while the second is still being
+//               exponentiated -- and rescales O only when the max grew by more than
+//               2^8 (exact: the stale max is carried into the final normalisation).
+//               Tiles strictly above the diagonal are skipped, the diagonal tile is
+//               masked element-wise.
 // Every mbarrier wait is bounded; on timeout the CTA raises a device error flag,
 // stops issuing work, and still releases its tensor memory before it exits.
 #include "common.cuh"
@@ -52,10 +57,10 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Params {
-    const int32_t* cu_seqlens;
-    const int32_t* items;  // [n_items] (seq << 16) | level, heaviest first; items[-1] slot holds the count
+    const int4* items;  // record 0: {number of (sequence, row block) pairs, 0, 0, 0}; record 1+i: {first token of the
+                        // sequence, its length, first row of the block, 0}, longest causal span first
     __nv_bfloat16* out;
-    int B, H, KVH, G;
+    int H, G;
     float scale_log2;
 };
 
@@ -131,6 +136,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+// 32 lanes x 16 columns, from the first 16 words of r.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+            taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -154,10 +169,10 @@ constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) 
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);  // B operand MN-major
 
 // ------------------------------------------------------------------------------------------
-// plan kernel: items sorted by row-block index, largest first
+// plan kernel: (sequence, 256-row block) pairs sorted by block index, largest first
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens, int B,
-                                                            int32_t* __restrict__ items_with_count, int capacity) {
+                                                            int4* __restrict__ items, int capacity) {
     __shared__ int hist[kMaxLevels];
     __shared__ int base[kMaxLevels];
     __shared__ int max_level;
@@ -183,16 +198,17 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
             base[l] = run;
             run += hist[l];
         }
-        items_with_count[0] = run < capacity ? run : capacity;
+        items[0] = make_int4(run < capacity ? run : capacity, 0, 0, 0);
     }
     __syncthreads();
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
-        const int len = cu_seqlens[b + 1] - cu_seqlens[b];
+        const int start = cu_seqlens[b];
+        const int len = cu_seqlens[b + 1] - start;
         int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
         if (n > kMaxLevels) n = kMaxLevels;
         for (int l = 0; l < n; ++l) {
             const int slot = atomicAdd(&base[l], 1);
-            if (slot < capacity) items_with_count[1 + slot] = (int32_t)(((uint32_t)b << 16) | (uint32_t)l);
+            if (slot < capacity) items[1 + slot] = make_int4(start, len, l * kBlockQ, 0);
         }
     }
 }
@@ -201,9 +217,9 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
 // main kernel
 // ------------------------------------------------------------------------------------------
 struct Shared {
-    uint64_t q_full;
+    uint64_t q_full, q_empty;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t s_full[2], p_full[2][2], o_full[2], o_empty[2];
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -214,6 +230,121 @@ __device__ __forceinline__ bool wait_or_abort(Shared* sh, uint64_t* bar, uint32_
     sh->abort_flag = 1;
     atomicOr(&g_error_flag, 4);
     return false;
+}
+
+struct Item {
+    int seq_start, len, q0, head;
+    int n_a, n_b, n_kv;  // KV tiles seen by Q tile A, by Q tile B (one more: its diagonal), and the larger
+};
+
+__device__ __forceinline__ Item load_item(const Params& p, int idx) {
+    Item it;
+    const int pair = idx / p.H;
+    it.head = idx - pair * p.H;
+    const int4 r = __ldg(p.items + 1 + pair);
+    it.seq_start = r.x;
+    it.len = r.y;
+    it.q0 = r.z;
+    const int rows = min(kBlockQ, it.len - it.q0);
+    it.n_a = it.q0 / kTileKV + 1;
+    it.n_b = rows > kTileQ ? it.q0 / kTileKV + 2 : 0;
+    it.n_kv = max(it.n_a, it.n_b);
+    return it;
+}
+
+// One 128-column S row -> running max, optional O rescale, bf16 P in two halves.  DIAG: key c visible iff c <= row.
+template <bool DIAG>
+__device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint32_t t_s, const uint32_t t_o,
+                                             const int row, const bool first, const uint32_t o_parity_prev,
+                                             const float scale_log2, float& m_run, float& m_used, float& l) {
+    uint32_t a[32], b[32];
+    // ---- pass 1: row max, chunk c+1 in flight while chunk c is reduced ----
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+    tmem_ld32(t_s, a);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? b : a;
+        uint32_t(&nxt)[32] = (c & 1) ? a : b;
+        tmem_ld32(t_s + ((c + 1) & 3) * 32, nxt);  // after the last chunk this re-loads chunk 0 for pass 2
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            float v0 = __uint_as_float(cur[i]), v1 = __uint_as_float(cur[i + 1]);
+            float v2 = __uint_as_float(cur[i + 2]), v3 = __uint_as_float(cur[i + 3]);
+            if (DIAG) {
+                v0 = (c * 32 + i > row) ? -INFINITY : v0;
+                v1 = (c * 32 + i + 1 > row) ? -INFINITY : v1;
+                v2 = (c * 32 + i + 2 > row) ? -INFINITY : v2;
+                v3 = (c * 32 + i + 3 > row) ? -INFINITY : v3;
+            }
+            mx0 = fmaxf(mx0, v0);
+            mx1 = fmaxf(mx1, v1);
+            mx2 = fmaxf(mx2, v2);
+            mx3 = fmaxf(mx3, v3);
+        }
+        tmem_wait_ld();
+    }
+    m_run = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+    if (first) {
+        m_used = m_run;
+    } else {
+        const bool grow = (m_run - m_used) * scale_log2 > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+            // O holds sums relative to m_used: bring it to m_run before this tile's P.V is added.
+            if (!wait_or_abort(sh, &sh->o_full[x], o_parity_prev)) return false;
+            tc_fence_after();
+            const float f = fast_exp2((m_used - m_run) * scale_log2);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(t_o + c * 32, b);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) b[i] = __float_as_uint(__uint_as_float(b[i]) * f);
+                tmem_st32(t_o + c * 32, b);
+            }
+            tmem_wait_st();
+            l *= f;
+            m_used = m_run;
+        }
+    }
+    // ---- pass 2: p = 2^(s*scale - m) as bf16 pairs, written over S columns already consumed ----
+    // Chunk c (scores 32c..32c+31) becomes packed columns 16c..16c+15, always behind the read position.
+    const float neg = -m_used * scale_log2;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? b : a;
+        uint32_t(&nxt)[32] = (c & 1) ? a : b;
+        if (c < 3) tmem_ld32(t_s + (c + 1) * 32, nxt);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), scale_log2, neg));
+            float e1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), scale_log2, neg));
+            float e2 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 2]), scale_log2, neg));
+            float e3 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 3]), scale_log2, neg));
+            if (DIAG) {
+                e0 = (c * 32 + 2 * i > row) ? 0.f : e0;
+                e1 = (c * 32 + 2 * i + 1 > row) ? 0.f : e1;
+                e2 = (c * 32 + 2 * i + 2 > row) ? 0.f : e2;
+                e3 = (c * 32 + 2 * i + 3 > row) ? 0.f : e3;
+            }
+            s0 += e0;
+            s1 += e1;
+            s2 += e2;
+            s3 += e3;
+            cur[i] = pack_bf16(e0, e1);      // in place: word i <= 2i has been consumed
+            cur[i + 1] = pack_bf16(e2, e3);
+        }
+        tmem_st16(t_s + c * 16, cur);
+        if (c < 3) tmem_wait_ld();
+        if (c & 1) {  // a half of P (64 keys) is complete: release its four P.V k-steps
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh->p_full[x][c >> 1]);
+        }
+    }
+    l += (s0 + s1) + (s2 + s3);
+    return true;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -230,6 +361,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     if (tid == 0) {
         mbar_init(&sh->q_full, 1);
+        mbar_init(&sh->q_empty, 1);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&sh->k_full[s], 1);
             mbar_init(&sh->k_empty[s], 1);
@@ -238,8 +370,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sh->s_full[x], 1);
-            mbar_init(&sh->p_full[x], kTileQ);
+            mbar_init(&sh->p_full[x][0], kTileQ);
+            mbar_init(&sh->p_full[x][1], kTileQ);
             mbar_init(&sh->o_full[x], 1);
+            mbar_init(&sh->o_empty[x], kTileQ);
         }
         sh->abort_flag = 0;
         sh->tmem_base = 0xFFFFFFFFu;
@@ -260,225 +394,162 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     griddep_wait();  // the plan kernel's item list (and the caller's q/k/v) must be visible from here on
 
-    // ---- which item ----
-    const int n_items = p.items[0];
-    const int pair = blockIdx.x / p.H;
-    const int head = blockIdx.x - pair * p.H;
-    bool active = pair < n_items && tmem != 0xFFFFFFFFu;
-    int seq_start = 0, L = 0, q0 = 0;
-    if (active) {
-        const uint32_t it = (uint32_t)p.items[1 + pair];
-        const int b = (int)(it >> 16);
-        q0 = (int)(it & 0xFFFFu) * kBlockQ;
-        seq_start = p.cu_seqlens[b];
-        L = p.cu_seqlens[b + 1] - seq_start;
-        active = q0 < L;
-    }
-    const int rows = active ? min(kBlockQ, L - q0) : 0;
-    const int n_a = active ? q0 / kTileKV + 1 : 0;                       // KV tiles seen by Q tile A
-    const int n_b = (active && rows > kTileQ) ? q0 / kTileKV + 2 : 0;    // ... by Q tile B (one more: its diagonal)
-    const int n_kv = max(n_a, n_b);
-    const int kvh = head / p.G;
+    const int total = (tmem != 0xFFFFFFFFu) ? p.items[0].x * p.H : 0;
+    const int first_idx = blockIdx.x, stride = gridDim.x;
 
     if (warp == 0) {
         // =============================== TMA producer ===============================
-        if (lane == 0 && active) {
-            const int tok_q = seq_start + q0;
-            mbar_expect_tx(&sh->q_full, (n_b > 0 ? 2 : 1) * kTileBytes);
-            tma_load_3d(sQ, &tm_q, &sh->q_full, 0, head, tok_q);
-            tma_load_3d(sQ + kPanelBytes, &tm_q, &sh->q_full, 64, head, tok_q);
-            if (n_b > 0) {
-                tma_load_3d(sQ + kTileBytes, &tm_q, &sh->q_full, 0, head, tok_q + kTileQ);
-                tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, head, tok_q + kTileQ);
-            }
-            for (int j = 0; j < n_kv; ++j) {
-                const int st = j % kStages;
-                const uint32_t par = ((j / kStages) & 1u) ^ 1u;
-                const int tok = seq_start + j * kTileKV;
-                if (!wait_or_abort(sh, &sh->k_empty[st], par)) break;
-                mbar_expect_tx(&sh->k_full[st], kTileBytes);
-                tma_load_3d(sK + st * kTileBytes, &tm_k, &sh->k_full[st], 0, kvh, tok);
-                tma_load_3d(sK + st * kTileBytes + kPanelBytes, &tm_k, &sh->k_full[st], 64, kvh, tok);
-                if (!wait_or_abort(sh, &sh->v_empty[st], par)) break;
-                mbar_expect_tx(&sh->v_full[st], kTileBytes);
-                tma_load_3d(sV + st * kTileBytes, &tm_v, &sh->v_full[st], 0, kvh, tok);
-                tma_load_3d(sV + st * kTileBytes + kPanelBytes, &tm_v, &sh->v_full[st], 64, kvh, tok);
+        if (lane == 0) {
+            uint32_t kt = 0;
+            int i = 0;
+            bool ok = true;
+            for (int idx = first_idx; ok && idx < total; idx += stride, ++i) {
+                const Item it = load_item(p, idx);
+                const int kvh = it.head / p.G;
+                const int tok_q = it.seq_start + it.q0;
+                if (i > 0 && !(ok = wait_or_abort(sh, &sh->q_empty, (i - 1) & 1u))) break;
+                mbar_expect_tx(&sh->q_full, (it.n_b > 0 ? 2 : 1) * kTileBytes);
+                tma_load_3d(sQ, &tm_q, &sh->q_full, 0, it.head, tok_q);
+                tma_load_3d(sQ + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q);
+                if (it.n_b > 0) {
+                    tma_load_3d(sQ + kTileBytes, &tm_q, &sh->q_full, 0, it.head, tok_q + kTileQ);
+                    tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q + kTileQ);
+                }
+                for (int j = 0; j < it.n_kv; ++j, ++kt) {
+                    const int st = kt % kStages;
+                    const uint32_t par = ((kt / kStages) & 1u) ^ 1u;
+                    const int tok = it.seq_start + j * kTileKV;
+                    if (!(ok = wait_or_abort(sh, &sh->k_empty[st], par))) break;
+                    mbar_expect_tx(&sh->k_full[st], kTileBytes);
+                    tma_load_3d(sK + st * kTileBytes, &tm_k, &sh->k_full[st], 0, kvh, tok);
+                    tma_load_3d(sK + st * kTileBytes + kPanelBytes, &tm_k, &sh->k_full[st], 64, kvh, tok);
+                    if (!(ok = wait_or_abort(sh, &sh->v_empty[st], par))) break;
+                    mbar_expect_tx(&sh->v_full[st], kTileBytes);
+                    tma_load_3d(sV + st * kTileBytes, &tm_v, &sh->v_full[st], 0, kvh, tok);
+                    tma_load_3d(sV + st * kTileBytes + kPanelBytes, &tm_v, &sh->v_full[st], 64, kvh, tok);
+                }
             }
         }
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
-        if (lane == 0 && active) {
+        if (lane == 0) {
             const uint32_t qa = smem_u32(sQ), qb = smem_u32(sQ + kTileBytes);
-            const uint32_t s_a = tmem, s_b = tmem + 128, o_a = tmem + 256, o_b = tmem + 384;
-            bool ok = wait_or_abort(sh, &sh->q_full, 0) && wait_or_abort(sh, &sh->k_full[0], 0);
-            if (ok) {
+            const uint32_t s_t[2] = {tmem, tmem + 128}, o_t[2] = {tmem + 256, tmem + 384};
+            const uint32_t q_s[2] = {qa, qb};
+            uint32_t kt = 0;             // K/V ring position at the start of the item
+            uint32_t tiles[2] = {0, 0};  // tiles finished per Q tile, over all items (barrier phases)
+            uint32_t used[2] = {0, 0};   // items in which the Q tile was active (o_empty phases)
+            int i = 0;
+            bool ok = true;
+
+            auto issue_qk = [&](int x, uint32_t kaddr) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ss(s_t[x], kmajor_desc(q_s[x], ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
+                tc_commit(&sh->s_full[x]);
+            };
+            auto issue_pv = [&](int x, int j, uint32_t vaddr) -> bool {
+                if (j == 0 && used[x] > 0 && !wait_or_abort(sh, &sh->o_empty[x], (used[x] - 1) & 1u)) return false;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    if (!wait_or_abort(sh, &sh->p_full[x][half], tiles[x] & 1u)) return false;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = half * 4; ks < half * 4 + 4; ++ks)
+                        mma_ts(o_t[x], s_t[x] + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
+                }
+                tc_commit(&sh->o_full[x]);
+                ++tiles[x];
+                return true;
+            };
+
+            for (int idx = first_idx; ok && idx < total; idx += stride, ++i) {
+                const Item it = load_item(p, idx);
+                const int n_x[2] = {it.n_a, it.n_b};
+                if (!(ok = wait_or_abort(sh, &sh->q_full, i & 1u))) break;
+                if (!(ok = wait_or_abort(sh, &sh->k_full[kt % kStages], (kt / kStages) & 1u))) break;
                 tc_fence_after();
-                const uint32_t k0 = smem_u32(sK);
+                issue_qk(0, smem_u32(sK + (kt % kStages) * kTileBytes));
+                if (it.n_b > 0) issue_qk(1, smem_u32(sK + (kt % kStages) * kTileBytes));
+                tc_commit(&sh->k_empty[kt % kStages]);
+                if (it.n_kv == 1) tc_commit(&sh->q_empty);
+                for (int j = 0; ok && j < it.n_kv; ++j) {
+                    const uint32_t cur = kt + j, nxt = cur + 1;
+                    const uint32_t vaddr = smem_u32(sV + (cur % kStages) * kTileBytes);
+                    const uint32_t kaddr = smem_u32(sK + (nxt % kStages) * kTileBytes);
+                    if (!(ok = wait_or_abort(sh, &sh->v_full[cur % kStages], (cur / kStages) & 1u))) break;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) mma_ss(s_a, kmajor_desc(qa, ks), kmajor_desc(k0, ks), kIdescQK, ks > 0);
-                tc_commit(&sh->s_full[0]);
-                if (n_b > 0) {
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_ss(s_b, kmajor_desc(qb, ks), kmajor_desc(k0, ks), kIdescQK, ks > 0);
-                    tc_commit(&sh->s_full[1]);
+                    for (int x = 0; x < 2; ++x) {
+                        if (j < n_x[x]) {
+                            if (!(ok = issue_pv(x, j, vaddr))) break;
+                        }
+                        if (x == 1) tc_commit(&sh->v_empty[cur % kStages]);
+                        if (j + 1 < n_x[x]) {
+                            if (!(ok = wait_or_abort(sh, &sh->k_full[nxt % kStages], (nxt / kStages) & 1u))) break;
+                            tc_fence_after();
+                            issue_qk(x, kaddr);
+                        }
+                    }
+                    if (!ok) break;
+                    if (j + 1 < it.n_kv) {
+                        tc_commit(&sh->k_empty[nxt % kStages]);
+                        if (j + 2 == it.n_kv) tc_commit(&sh->q_empty);  // the item's last Q.K^T has been issued
+                    }
                 }
-                tc_commit(&sh->k_empty[0]);
-            }
-            for (int j = 0; ok && j < n_kv; ++j) {
-                const int st = j % kStages, stn = (j + 1) % kStages;
-                const uint32_t vaddr = smem_u32(sV + st * kTileBytes);
-                const uint32_t kaddr = smem_u32(sK + stn * kTileBytes);
-                if (!(ok = wait_or_abort(sh, &sh->v_full[st], (j / kStages) & 1u))) break;
-                if (j < n_a) {
-                    if (!(ok = wait_or_abort(sh, &sh->p_full[0], j & 1u))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_ts(o_a, s_a + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
-                    tc_commit(&sh->o_full[0]);
-                }
-                if (j + 1 < n_a) {
-                    if (!(ok = wait_or_abort(sh, &sh->k_full[stn], ((j + 1) / kStages) & 1u))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_ss(s_a, kmajor_desc(qa, ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
-                    tc_commit(&sh->s_full[0]);
-                }
-                if (j < n_b) {
-                    if (!(ok = wait_or_abort(sh, &sh->p_full[1], j & 1u))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_ts(o_b, s_b + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
-                    tc_commit(&sh->o_full[1]);
-                }
-                tc_commit(&sh->v_empty[st]);
-                if (j + 1 < n_b) {
-                    if (!(ok = wait_or_abort(sh, &sh->k_full[stn], ((j + 1) / kStages) & 1u))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_ss(s_b, kmajor_desc(qb, ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
-                    tc_commit(&sh->s_full[1]);
-                }
-                if (j + 1 < n_kv) tc_commit(&sh->k_empty[stn]);
+                used[0] += 1;
+                used[1] += it.n_b > 0 ? 1 : 0;
+                kt += it.n_kv;
             }
         }
     } else if (warp >= 4) {
         // ============================ softmax warpgroups ============================
         const int x = (warp - 4) >> 2;              // 0: tile A, 1: tile B
-        const int n_x = x == 0 ? n_a : n_b;
         const int quarter = warp & 3;               // tensor-memory lane quarter this warp may touch
         const int row = quarter * 32 + lane;        // row within the Q tile
-        const int q_pos = q0 + x * kTileQ + row;    // position within the sequence
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem + x * 128 + lane_base;
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
-        float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
+        uint32_t tiles = 0;  // tiles finished by this Q tile over all items (barrier phases)
         bool ok = true;
-        for (int j = 0; ok && j < n_x; ++j) {
-            if (!(ok = wait_or_abort(sh, &sh->s_full[x], j & 1u))) break;
+        for (int idx = first_idx; ok && idx < total; idx += stride) {
+            const Item it = load_item(p, idx);
+            const int n_x = x == 0 ? it.n_a : it.n_b;
+            if (n_x == 0) continue;
+            const int q_pos = it.q0 + x * kTileQ + row;  // position within the sequence
+            float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
+            for (int j = 0; ok && j < n_x; ++j, ++tiles) {
+                if (!(ok = wait_or_abort(sh, &sh->s_full[x], tiles & 1u))) break;
+                tc_fence_after();
+                if (j == n_x - 1)
+                    ok = softmax_tile<true>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+                else
+                    ok = softmax_tile<false>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+            }
+            if (!ok) break;
+            // ---- epilogue: O / l -> bf16 -> global, then hand O back to the MMA thread ----
+            if (!(ok = wait_or_abort(sh, &sh->o_full[x], (tiles - 1) & 1u))) break;
             tc_fence_after();
-            const bool diagonal = (j == n_x - 1);  // key c of this tile is visible to row r iff c <= r
-            // pass 1: row max (tensor-memory reads are cheap; holding all 128 scores would spill registers)
-            float mx = -INFINITY;
+            const float inv = 1.0f / l;
+            __nv_bfloat16* orow = p.out + ((size_t)(it.seq_start + q_pos) * p.H + it.head) * kD;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t sv[32];
-                tmem_ld32(t_s + c * 32, sv);
+                uint32_t ov[32];
+                tmem_ld32(t_o + c * 32, ov);
                 tmem_wait_ld();
+                if (q_pos < it.len) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float v = __uint_as_float(sv[i]);
-                    mx = fmaxf(mx, (diagonal && c * 32 + i > row) ? -INFINITY : v);
-                }
-            }
-            m_run = fmaxf(m_run, mx);
-            if (j == 0) {
-                m_used = m_run;
-            } else {
-                const bool grow = (m_run - m_used) * p.scale_log2 > kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {
-                    // O holds sums relative to m_used: bring it to m_run before more is added.
-                    if (!(ok = wait_or_abort(sh, &sh->o_full[x], (j - 1) & 1u))) break;
-                    tc_fence_after();
-                    const float f = fast_exp2((m_used - m_run) * p.scale_log2);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t ov[32];
-                        tmem_ld32(t_o + c * 32, ov);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-                        tmem_st32(t_o + c * 32, ov);
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(ov[8 * i + 0]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
                     }
-                    tmem_wait_st();
-                    l *= f;
-                    m_used = m_run;
                 }
             }
-            // pass 2: p = 2^(s*scale - m), packed to bf16 pairs and written over the S columns already consumed
-            // (packed column 16c+i replaces scores 32c+2i, 32c+2i+1: always behind the read position).
-            const float neg = -m_used * p.scale_log2;
-            float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t sa[32], sb[32], pk[32];
-                tmem_ld32(t_s + half * 64, sa);
-                tmem_ld32(t_s + half * 64 + 32, sb);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int c0 = half * 64 + 2 * i, c1 = half * 64 + 32 + 2 * i;
-                    float a0 = fast_exp2(fmaf(__uint_as_float(sa[2 * i]), p.scale_log2, neg));
-                    float a1 = fast_exp2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale_log2, neg));
-                    float b0 = fast_exp2(fmaf(__uint_as_float(sb[2 * i]), p.scale_log2, neg));
-                    float b1 = fast_exp2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale_log2, neg));
-                    if (diagonal) {
-                        a0 = c0 > row ? 0.f : a0;
-                        a1 = c0 + 1 > row ? 0.f : a1;
-                        b0 = c1 > row ? 0.f : b0;
-                        b1 = c1 + 1 > row ? 0.f : b1;
-                    }
-                    sum0 += a0 + b0;
-                    sum1 += a1 + b1;
-                    pk[i] = pack_bf16(a0, a1);
-                    pk[16 + i] = pack_bf16(b0, b1);
-                }
-                tmem_st32(t_s + half * 32, pk);
-            }
-            l += sum0 + sum1;
-            tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->p_full[x]);
-        }
-        // ---- epilogue: O / l -> bf16 -> global ----
-        if (ok && n_x > 0) {
-            ok = wait_or_abort(sh, &sh->o_full[x], (n_x - 1) & 1u);
-            if (ok) {
-                tc_fence_after();
-                const float inv = 1.0f / l;
-                __nv_bfloat16* orow = p.out + ((size_t)(seq_start + q_pos) * p.H + head) * kD;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t ov[32];
-                    tmem_ld32(t_o + c * 32, ov);
-                    tmem_wait_ld();
-                    if (q_pos < L) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 w;
-                            w.x = pack_bf16(__uint_as_float(ov[8 * i + 0]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
-                            w.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
-                            w.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
-                            w.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
-                        }
-                    }
-                }
-            }
+            mbar_arrive(&sh->o_empty[x]);
         }
     }
 
@@ -540,7 +611,7 @@ extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, in
     (void)KVH;
     (void)D;
     if (T < 0 || B < 0) return 256;
-    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 4;
+    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 16;
     return (n + 255) & ~size_t(255);
 }
 
@@ -599,12 +670,9 @@ extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const voi
     if ((rc = make_map(&tm_v, v, KVH, T))) return rc;
 
     Params p;
-    p.cu_seqlens = cu_seqlens_q;
-    p.items = (const int32_t*)workspace;
+    p.items = (const int4*)workspace;
     p.out = (__nv_bfloat16*)out;
-    p.B = B;
     p.H = H;
-    p.KVH = KVH;
     p.G = H / KVH;
     p.scale_log2 = scale * 1.4426950408889634f;
 
@@ -618,8 +686,9 @@ extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const voi
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, B, (int32_t*)workspace, (int)cap));
-    cfg.gridDim = dim3((unsigned)(pairs * H));
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, B, (int4*)workspace, (int)cap));
+    const int64_t ctas = pairs * H < (int64_t)sm_count() ? pairs * H : (int64_t)sm_count();
+    cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, varlen_prefill_kernel, tm_q, tm_k, tm_v, p));
