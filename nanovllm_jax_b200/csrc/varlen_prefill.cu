@@ -136,14 +136,48 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 // 32 lanes x 16 columns, from the first 16 words of r.
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[32]) {
+template <int N>
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
             taddr),
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+// Packed fp32 pairs (one instruction, two lanes of math) and the three-input max of sm_100.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
@@ -253,36 +287,33 @@ __device__ __forceinline__ Item load_item(const Params& p, int idx) {
 }
 
 // One 128-column S row -> running max, optional O rescale, bf16 P in two halves.  DIAG: key c visible iff c <= row.
+// The whole row is held in registers (the softmax warpgroups raise their register budget with setmaxnreg), so
+// tensor memory is read once and its latency is paid once per tile.
 template <bool DIAG>
 __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint32_t t_s, const uint32_t t_o,
                                              const int row, const bool first, const uint32_t o_parity_prev,
                                              const float scale_log2, float& m_run, float& m_used, float& l) {
-    uint32_t a[32], b[32];
-    // ---- pass 1: row max, chunk c+1 in flight while chunk c is reduced ----
-    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-    tmem_ld32(t_s, a);
+    uint32_t v[4][32];
+    tmem_ld32(t_s, v[0]);
+    tmem_ld32(t_s + 32, v[1]);
+    tmem_ld32(t_s + 64, v[2]);
+    tmem_ld32(t_s + 96, v[3]);
     tmem_wait_ld();
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? b : a;
-        uint32_t(&nxt)[32] = (c & 1) ? a : b;
-        tmem_ld32(t_s + ((c + 1) & 3) * 32, nxt);  // after the last chunk this re-loads chunk 0 for pass 2
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-            float v0 = __uint_as_float(cur[i]), v1 = __uint_as_float(cur[i + 1]);
-            float v2 = __uint_as_float(cur[i + 2]), v3 = __uint_as_float(cur[i + 3]);
-            if (DIAG) {
-                v0 = (c * 32 + i > row) ? -INFINITY : v0;
-                v1 = (c * 32 + i + 1 > row) ? -INFINITY : v1;
-                v2 = (c * 32 + i + 2 > row) ? -INFINITY : v2;
-                v3 = (c * 32 + i + 3 > row) ? -INFINITY : v3;
+        for (int i = 0; i < 32; i += 8) {
+            if (DIAG) {  // mask in place so that the second pass needs no select
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (c * 32 + i + u > row) v[c][i + u] = 0xFF800000u;
             }
-            mx0 = fmaxf(mx0, v0);
-            mx1 = fmaxf(mx1, v1);
-            mx2 = fmaxf(mx2, v2);
-            mx3 = fmaxf(mx3, v3);
+            mx0 = max3(mx0, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(v[c][i + 2]), __uint_as_float(v[c][i + 3]));
+            mx2 = max3(mx2, __uint_as_float(v[c][i + 4]), __uint_as_float(v[c][i + 5]));
+            mx3 = max3(mx3, __uint_as_float(v[c][i + 6]), __uint_as_float(v[c][i + 7]));
         }
-        tmem_wait_ld();
     }
     m_run = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
     if (first) {
@@ -294,55 +325,51 @@ __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint
             if (!wait_or_abort(sh, &sh->o_full[x], o_parity_prev)) return false;
             tc_fence_after();
             const float f = fast_exp2((m_used - m_run) * scale_log2);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(t_o + c * 32, b);
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+                uint32_t ov[16];
+                tmem_ld16(t_o + c * 16, ov);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) b[i] = __float_as_uint(__uint_as_float(b[i]) * f);
-                tmem_st32(t_o + c * 32, b);
+                for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+                tmem_st16(t_o + c * 16, ov);
             }
             tmem_wait_st();
             l *= f;
             m_used = m_run;
         }
     }
-    // ---- pass 2: p = 2^(s*scale - m) as bf16 pairs, written over S columns already consumed ----
-    // Chunk c (scores 32c..32c+31) becomes packed columns 16c..16c+15, always behind the read position.
+    // p = 2^(s*scale - m) as bf16 pairs, written over the S columns (all of them are in registers by now):
+    // chunk c (scores 32c..32c+31) becomes packed columns 16c..16c+15.
     const float neg = -m_used * scale_log2;
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    const uint64_t scale2 = pack2(scale_log2, scale_log2), neg2 = pack2(neg, neg);
+    uint64_t acc_a = pack2(0.f, 0.f), acc_b = pack2(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? b : a;
-        uint32_t(&nxt)[32] = (c & 1) ? a : b;
-        if (c < 3) tmem_ld32(t_s + (c + 1) * 32, nxt);
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-            float e0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), scale_log2, neg));
-            float e1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), scale_log2, neg));
-            float e2 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 2]), scale_log2, neg));
-            float e3 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 3]), scale_log2, neg));
-            if (DIAG) {
-                e0 = (c * 32 + 2 * i > row) ? 0.f : e0;
-                e1 = (c * 32 + 2 * i + 1 > row) ? 0.f : e1;
-                e2 = (c * 32 + 2 * i + 2 > row) ? 0.f : e2;
-                e3 = (c * 32 + 2 * i + 3 > row) ? 0.f : e3;
-            }
-            s0 += e0;
-            s1 += e1;
-            s2 += e2;
-            s3 += e3;
-            cur[i] = pack_bf16(e0, e1);      // in place: word i <= 2i has been consumed
-            cur[i + 1] = pack_bf16(e2, e3);
+            float x0, x1, x2, x3;
+            unpack2(fma2(pack2(__uint_as_float(v[c][2 * i]), __uint_as_float(v[c][2 * i + 1])), scale2, neg2), x0, x1);
+            unpack2(fma2(pack2(__uint_as_float(v[c][2 * i + 2]), __uint_as_float(v[c][2 * i + 3])), scale2, neg2), x2,
+                    x3);
+            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);  // 2^-inf = 0 for masked keys
+            const float e2 = fast_exp2(x2), e3 = fast_exp2(x3);
+            acc_a = add2(acc_a, pack2(e0, e1));
+            acc_b = add2(acc_b, pack2(e2, e3));
+            v[c][i] = pack_bf16(e0, e1);  // in place: word i <= 2i has been consumed
+            v[c][i + 1] = pack_bf16(e2, e3);
         }
-        tmem_st16(t_s + c * 16, cur);
-        if (c < 3) tmem_wait_ld();
+        tmem_st16(t_s + c * 16, v[c]);
         if (c & 1) {  // a half of P (64 keys) is complete: release its four P.V k-steps
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sh->p_full[x][c >> 1]);
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(&sh->p_full[x][c >> 1]);
         }
     }
+    float s0, s1, s2, s3;
+    unpack2(acc_a, s0, s1);
+    unpack2(acc_b, s2, s3);
     l += (s0 + s1) + (s2 + s3);
     return true;
 }
@@ -370,10 +397,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sh->s_full[x], 1);
-            mbar_init(&sh->p_full[x][0], kTileQ);
-            mbar_init(&sh->p_full[x][1], kTileQ);
+            mbar_init(&sh->p_full[x][0], kTileQ / 32);  // one arrival per softmax warp
+            mbar_init(&sh->p_full[x][1], kTileQ / 32);
             mbar_init(&sh->o_full[x], 1);
-            mbar_init(&sh->o_empty[x], kTileQ);
+            mbar_init(&sh->o_empty[x], kTileQ / 32);
         }
         sh->abort_flag = 0;
         sh->tmem_base = 0xFFFFFFFFu;
@@ -394,9 +421,13 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     griddep_wait();  // the plan kernel's item list (and the caller's q/k/v) must be visible from here on
 
+    // Register budget: the TMA / MMA warpgroup keeps 96 registers per thread, the two softmax warpgroups take 200
+    // (96*128 + 200*256 <= 64K), enough to hold a whole 128-column score row.
     const int total = (tmem != 0xFFFFFFFFu) ? p.items[0].x * p.H : 0;
     const int first_idx = blockIdx.x, stride = gridDim.x;
 
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp == 0) {
         // =============================== TMA producer ===============================
         if (lane == 0) {
@@ -433,22 +464,28 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
         if (lane == 0) {
-            const uint32_t qa = smem_u32(sQ), qb = smem_u32(sQ + kTileBytes);
+            // Descriptors are built once: per k-step only the 14-bit start-address field (bytes >> 4) moves, by a
+            // compile-time constant, so issuing an MMA costs one 32-bit add instead of a descriptor rebuild.
             const uint32_t s_t[2] = {tmem, tmem + 128}, o_t[2] = {tmem + 256, tmem + 384};
-            const uint32_t q_s[2] = {qa, qb};
+            const uint64_t q_desc[2] = {kmajor_desc(smem_u32(sQ), 0), kmajor_desc(smem_u32(sQ + kTileBytes), 0)};
+            static_assert(kStages == 2, "descriptor selects below assume a two-stage ring");
+            const uint64_t k_desc0 = kmajor_desc(smem_u32(sK), 0), k_desc1 = kmajor_desc(smem_u32(sK + kTileBytes), 0);
+            const uint64_t v_desc0 = mnmajor_desc(smem_u32(sV), 0), v_desc1 = mnmajor_desc(smem_u32(sV + kTileBytes), 0);
             uint32_t kt = 0;             // K/V ring position at the start of the item
             uint32_t tiles[2] = {0, 0};  // tiles finished per Q tile, over all items (barrier phases)
             uint32_t used[2] = {0, 0};   // items in which the Q tile was active (o_empty phases)
             int i = 0;
             bool ok = true;
 
-            auto issue_qk = [&](int x, uint32_t kaddr) {
+            auto issue_qk = [&](int x, uint64_t kd) {
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_ss(s_t[x], kmajor_desc(q_s[x], ks), kmajor_desc(kaddr, ks), kIdescQK, ks > 0);
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t step = (uint32_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
+                    mma_ss(s_t[x], q_desc[x] + step, kd + step, kIdescQK, ks > 0);
+                }
                 tc_commit(&sh->s_full[x]);
             };
-            auto issue_pv = [&](int x, int j, uint32_t vaddr) -> bool {
+            auto issue_pv = [&](int x, int j, uint64_t vd) -> bool {
                 if (j == 0 && used[x] > 0 && !wait_or_abort(sh, &sh->o_empty[x], (used[x] - 1) & 1u)) return false;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -456,7 +493,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tc_fence_after();
 #pragma unroll
                     for (int ks = half * 4; ks < half * 4 + 4; ++ks)
-                        mma_ts(o_t[x], s_t[x] + ks * 8, mnmajor_desc(vaddr, ks), kIdescPV, (j > 0 || ks > 0));
+                        mma_ts(o_t[x], s_t[x] + ks * 8, vd + (uint32_t)((ks * 16 * 128) >> 4), kIdescPV,
+                               (j > 0 || ks > 0));
                 }
                 tc_commit(&sh->o_full[x]);
                 ++tiles[x];
@@ -469,14 +507,14 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!(ok = wait_or_abort(sh, &sh->q_full, i & 1u))) break;
                 if (!(ok = wait_or_abort(sh, &sh->k_full[kt % kStages], (kt / kStages) & 1u))) break;
                 tc_fence_after();
-                issue_qk(0, smem_u32(sK + (kt % kStages) * kTileBytes));
-                if (it.n_b > 0) issue_qk(1, smem_u32(sK + (kt % kStages) * kTileBytes));
+                issue_qk(0, (kt & 1u) ? k_desc1 : k_desc0);
+                if (it.n_b > 0) issue_qk(1, (kt & 1u) ? k_desc1 : k_desc0);
                 tc_commit(&sh->k_empty[kt % kStages]);
                 if (it.n_kv == 1) tc_commit(&sh->q_empty);
                 for (int j = 0; ok && j < it.n_kv; ++j) {
                     const uint32_t cur = kt + j, nxt = cur + 1;
-                    const uint32_t vaddr = smem_u32(sV + (cur % kStages) * kTileBytes);
-                    const uint32_t kaddr = smem_u32(sK + (nxt % kStages) * kTileBytes);
+                    const uint64_t vaddr = (cur & 1u) ? v_desc1 : v_desc0;
+                    const uint64_t kaddr = (nxt & 1u) ? k_desc1 : k_desc0;
                     if (!(ok = wait_or_abort(sh, &sh->v_full[cur % kStages], (cur / kStages) & 1u))) break;
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
@@ -501,7 +539,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 kt += it.n_kv;
             }
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         // ============================ softmax warpgroups ============================
         const int x = (warp - 4) >> 2;              // 0: tile A, 1: tile B
         const int quarter = warp & 3;               // tensor-memory lane quarter this warp may touch
@@ -549,7 +589,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
             }
             tc_fence_before();
-            mbar_arrive(&sh->o_empty[x]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->o_empty[x]);
         }
     }
 
