@@ -15,13 +15,17 @@
 //
 // Per CTA (12 warps = 3 warpgroups; the first gives registers away with setmaxnreg, the softmax
 // warpgroups take them):
-//   warp 0      TMA producer: Q tiles once, then K and V tiles [128 tokens x 128 dims]
-//               through two-stage mbarrier rings (cp.async.bulk.tensor, 128-byte
-//               swizzle, no multicast).
-//   warp 1      MMA issuer: S = Q K^T (operands in shared memory) and O += P V (P read
-//               from tensor memory, V from shared memory, MN-major), M = N = 128,
-//               K = 16 per instruction; tcgen05.commit signals the mbarriers.  Also
-//               owns the tensor-memory allocation (512 columns: S_A S_B O_A O_B).
+//   warp 0      TMA producer: Q tiles once per item, then K and V tiles [128 tokens x
+//               128 dims] through one five-slot mbarrier ring filled K0 V0 K1 V1 ...
+//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast): K(j+2) takes the
+//               slot V(j-1) leaves and V(j+2) the slot K(j) leaves, so every tile is
+//               requested about two tiles before it is needed -- the kernel is bound by
+//               the latency of these loads unless that much is in flight.
+//   warps 1, 2  MMA issuers, one thread each for Q tile A and Q tile B: S = Q K^T
+//               (operands in shared memory) and O += P V (P read from tensor memory, V
+//               from shared memory, MN-major), M = N = 128, K = 16 per instruction;
+//               tcgen05.commit signals the mbarriers.  Warp 1 also owns the tensor-
+//               memory allocation (512 columns: S_A S_B O_A O_B).
 //   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row
 //               reads its S row from tensor memory (32-column chunks, the next chunk
 //               in flight while the current one is processed), keeps the running
@@ -49,9 +53,9 @@ constexpr int kTileKV = 128;
 constexpr int kThreads = 384;            // 3 warpgroups: {TMA, MMA, 2 idle warps} | softmax A | softmax B
 constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 dims bf16, 128B-swizzled
 constexpr int kTileBytes = 2 * kPanelBytes;
-constexpr int kStages = 2;
-constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;  // Q_A Q_B | K ring | V ring
-constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
+constexpr int kSlots = 5;                // one ring for K and V tiles, filled in the order K0 V0 K1 V1 ...
+constexpr int kSmemTiles = (2 + kSlots) * kTileBytes;  // Q_A Q_B | K/V ring  (224 KB)
+constexpr int kSmemBytes = kSmemTiles + 512 + 1024;
 constexpr int kMaxLevels = 2048;       // row blocks per sequence the plan kernel can rank
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -252,8 +256,9 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
 // ------------------------------------------------------------------------------------------
 struct Shared {
     uint64_t q_full, q_empty;
-    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t kv_full[kSlots], kv_empty[kSlots];
     uint64_t s_full[2], p_full[2][2], o_full[2], o_empty[2];
+    uint64_t turn[2];  // softmax ping-pong: turn[0] = "tile A finished a softmax", turn[1] = "tile B finished one"
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -380,20 +385,17 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                                   // [2][tile]
-    uint8_t* sK = smem + 2 * kTileBytes;                  // [kStages][tile]
-    uint8_t* sV = sK + kStages * kTileBytes;              // [kStages][tile]
+    uint8_t* sKV = smem + 2 * kTileBytes;                 // [kSlots][tile]: ring position 2j holds K(j), 2j+1 holds V(j)
     Shared* sh = reinterpret_cast<Shared*>(smem + kSmemTiles);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
         mbar_init(&sh->q_full, 1);
-        mbar_init(&sh->q_empty, 1);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&sh->k_full[s], 1);
-            mbar_init(&sh->k_empty[s], 1);
-            mbar_init(&sh->v_full[s], 1);
-            mbar_init(&sh->v_empty[s], 1);
+        mbar_init(&sh->q_empty, 2);   // both MMA issuers
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(&sh->kv_full[s], 1);
+            mbar_init(&sh->kv_empty[s], 2);  // both MMA issuers
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sh->s_full[x], 1);
@@ -401,6 +403,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(&sh->p_full[x][1], kTileQ / 32);
             mbar_init(&sh->o_full[x], 1);
             mbar_init(&sh->o_empty[x], kTileQ / 32);
+            mbar_init(&sh->turn[x], kTileQ / 32);
         }
         sh->abort_flag = 0;
         sh->tmem_base = 0xFFFFFFFFu;
@@ -447,95 +450,107 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q + kTileQ);
                 }
                 for (int j = 0; j < it.n_kv; ++j, ++kt) {
-                    const int st = kt % kStages;
-                    const uint32_t par = ((kt / kStages) & 1u) ^ 1u;
                     const int tok = it.seq_start + j * kTileKV;
-                    if (!(ok = wait_or_abort(sh, &sh->k_empty[st], par))) break;
-                    mbar_expect_tx(&sh->k_full[st], kTileBytes);
-                    tma_load_3d(sK + st * kTileBytes, &tm_k, &sh->k_full[st], 0, kvh, tok);
-                    tma_load_3d(sK + st * kTileBytes + kPanelBytes, &tm_k, &sh->k_full[st], 64, kvh, tok);
-                    if (!(ok = wait_or_abort(sh, &sh->v_empty[st], par))) break;
-                    mbar_expect_tx(&sh->v_full[st], kTileBytes);
-                    tma_load_3d(sV + st * kTileBytes, &tm_v, &sh->v_full[st], 0, kvh, tok);
-                    tma_load_3d(sV + st * kTileBytes + kPanelBytes, &tm_v, &sh->v_full[st], 64, kvh, tok);
+#pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {  // K(j) then V(j): with five slots both are requested ~2 tiles ahead
+                        const uint32_t pos = 2 * kt + kv;
+                        const int slot = pos % kSlots;
+                        if (!(ok = wait_or_abort(sh, &sh->kv_empty[slot], ((pos / kSlots) & 1u) ^ 1u))) break;
+                        const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
+                        mbar_expect_tx(&sh->kv_full[slot], kTileBytes);
+                        tma_load_3d(sKV + slot * kTileBytes, tm, &sh->kv_full[slot], 0, kvh, tok);
+                        tma_load_3d(sKV + slot * kTileBytes + kPanelBytes, tm, &sh->kv_full[slot], 64, kvh, tok);
+                    }
+                    if (!ok) break;
                 }
             }
         }
-    } else if (warp == 1) {
-        // ================================ MMA issuer ================================
+    } else if (warp == 1 || warp == 2) {
+        // ============================== MMA issuers ===============================
+        // One issuing thread per Q tile (warp 1: tile A, warp 2: tile B).  An issuing thread blocks on every
+        // tcgen05.mma until the tensor pipe accepts it and pays a couple of hundred cycles for every barrier it
+        // polls; with two independent issuers one tile's bookkeeping hides behind the other tile's MMAs.  Each
+        // thread owns its tile's S / P / O barriers; the shared K/V ring slots and the Q buffer are released by
+        // both (their "empty" barriers count two arrivals: a tcgen05.commit from a thread that read the slot, a
+        // plain arrive from a thread whose tile does not need it).
         if (lane == 0) {
-            // Descriptors are built once: per k-step only the 14-bit start-address field (bytes >> 4) moves, by a
-            // compile-time constant, so issuing an MMA costs one 32-bit add instead of a descriptor rebuild.
-            const uint32_t s_t[2] = {tmem, tmem + 128}, o_t[2] = {tmem + 256, tmem + 384};
-            const uint64_t q_desc[2] = {kmajor_desc(smem_u32(sQ), 0), kmajor_desc(smem_u32(sQ + kTileBytes), 0)};
-            static_assert(kStages == 2, "descriptor selects below assume a two-stage ring");
-            const uint64_t k_desc0 = kmajor_desc(smem_u32(sK), 0), k_desc1 = kmajor_desc(smem_u32(sK + kTileBytes), 0);
-            const uint64_t v_desc0 = mnmajor_desc(smem_u32(sV), 0), v_desc1 = mnmajor_desc(smem_u32(sV + kTileBytes), 0);
-            uint32_t kt = 0;             // K/V ring position at the start of the item
-            uint32_t tiles[2] = {0, 0};  // tiles finished per Q tile, over all items (barrier phases)
-            uint32_t used[2] = {0, 0};   // items in which the Q tile was active (o_empty phases)
+            const int x = warp - 1;
+            const uint32_t s_t = tmem + x * 128, o_t = tmem + 256 + x * 128;
+            // Descriptors are built once: per k-step and per ring slot only the 14-bit start-address field
+            // (bytes >> 4) moves, so issuing an MMA costs one 32-bit add instead of a descriptor rebuild.
+            const uint64_t q_desc = kmajor_desc(smem_u32(sQ + x * kTileBytes), 0);
+            const uint64_t k_desc0 = kmajor_desc(smem_u32(sKV), 0), v_desc0 = mnmajor_desc(smem_u32(sKV), 0);
+            constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);  // next ring slot, in descriptor address units
+            uint32_t kt = 0;     // K/V tiles consumed before this item
+            uint32_t tiles = 0;  // tiles finished by this Q tile, over all items (barrier phases)
+            uint32_t used = 0;   // items in which this Q tile was active (o_empty phases)
             int i = 0;
             bool ok = true;
 
-            auto issue_qk = [&](int x, uint64_t kd) {
+            auto issue_qk = [&](uint64_t kd) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t step = (uint32_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
-                    mma_ss(s_t[x], q_desc[x] + step, kd + step, kIdescQK, ks > 0);
+                    mma_ss(s_t, q_desc + step, kd + step, kIdescQK, ks > 0);
                 }
                 tc_commit(&sh->s_full[x]);
             };
-            auto issue_pv = [&](int x, int j, uint64_t vd) -> bool {
-                if (j == 0 && used[x] > 0 && !wait_or_abort(sh, &sh->o_empty[x], (used[x] - 1) & 1u)) return false;
+            auto issue_pv = [&](int j, uint64_t vd) -> bool {
+                if (j == 0 && used > 0 && !wait_or_abort(sh, &sh->o_empty[x], (used - 1) & 1u)) return false;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    if (!wait_or_abort(sh, &sh->p_full[x][half], tiles[x] & 1u)) return false;
+                    if (!wait_or_abort(sh, &sh->p_full[x][half], tiles & 1u)) return false;
                     tc_fence_after();
 #pragma unroll
                     for (int ks = half * 4; ks < half * 4 + 4; ++ks)
-                        mma_ts(o_t[x], s_t[x] + ks * 8, vd + (uint32_t)((ks * 16 * 128) >> 4), kIdescPV,
-                               (j > 0 || ks > 0));
+                        mma_ts(o_t, s_t + ks * 8, vd + (uint32_t)((ks * 16 * 128) >> 4), kIdescPV, (j > 0 || ks > 0));
                 }
                 tc_commit(&sh->o_full[x]);
-                ++tiles[x];
+                ++tiles;
                 return true;
             };
+            // the slot holding ring position pos: K(j) sits at 2j, V(j) at 2j+1
+            auto slot_full = [&](uint32_t pos) { return wait_or_abort(sh, &sh->kv_full[pos % kSlots], (pos / kSlots) & 1u); };
 
             for (int idx = first_idx; ok && idx < total; idx += stride, ++i) {
                 const Item it = load_item(p, idx);
-                const int n_x[2] = {it.n_a, it.n_b};
+                const int n_x = x == 0 ? it.n_a : it.n_b;
                 if (!(ok = wait_or_abort(sh, &sh->q_full, i & 1u))) break;
-                if (!(ok = wait_or_abort(sh, &sh->k_full[kt % kStages], (kt / kStages) & 1u))) break;
-                tc_fence_after();
-                issue_qk(0, (kt & 1u) ? k_desc1 : k_desc0);
-                if (it.n_b > 0) issue_qk(1, (kt & 1u) ? k_desc1 : k_desc0);
-                tc_commit(&sh->k_empty[kt % kStages]);
-                if (it.n_kv == 1) tc_commit(&sh->q_empty);
-                for (int j = 0; ok && j < it.n_kv; ++j) {
-                    const uint32_t cur = kt + j, nxt = cur + 1;
-                    const uint64_t vaddr = (cur & 1u) ? v_desc1 : v_desc0;
-                    const uint64_t kaddr = (nxt & 1u) ? k_desc1 : k_desc0;
-                    if (!(ok = wait_or_abort(sh, &sh->v_full[cur % kStages], (cur / kStages) & 1u))) break;
-#pragma unroll
-                    for (int x = 0; x < 2; ++x) {
-                        if (j < n_x[x]) {
-                            if (!(ok = issue_pv(x, j, vaddr))) break;
-                        }
-                        if (x == 1) tc_commit(&sh->v_empty[cur % kStages]);
-                        if (j + 1 < n_x[x]) {
-                            if (!(ok = wait_or_abort(sh, &sh->k_full[nxt % kStages], (nxt / kStages) & 1u))) break;
-                            tc_fence_after();
-                            issue_qk(x, kaddr);
-                        }
-                    }
-                    if (!ok) break;
-                    if (j + 1 < it.n_kv) {
-                        tc_commit(&sh->k_empty[nxt % kStages]);
-                        if (j + 2 == it.n_kv) tc_commit(&sh->q_empty);  // the item's last Q.K^T has been issued
+                if (n_x == 0) mbar_arrive(&sh->q_empty);  // this tile never reads the Q buffer of this item
+                {
+                    const uint32_t kpos = 2 * kt;
+                    if (!(ok = slot_full(kpos))) break;
+                    if (n_x > 0) {
+                        tc_fence_after();
+                        issue_qk(k_desc0 + (kpos % kSlots) * kSlotStep);
+                        tc_commit(&sh->kv_empty[kpos % kSlots]);
+                        if (n_x == 1) tc_commit(&sh->q_empty);
+                    } else {
+                        mbar_arrive(&sh->kv_empty[kpos % kSlots]);
                     }
                 }
-                used[0] += 1;
-                used[1] += it.n_b > 0 ? 1 : 0;
+                for (int j = 0; ok && j < it.n_kv; ++j) {
+                    const uint32_t vpos = 2 * (kt + j) + 1, kpos = vpos + 1;  // ring positions of V(j) and K(j+1)
+                    if (!(ok = slot_full(vpos))) break;
+                    if (j < n_x) {
+                        if (!(ok = issue_pv(j, v_desc0 + (vpos % kSlots) * kSlotStep))) break;
+                        tc_commit(&sh->kv_empty[vpos % kSlots]);
+                    } else {
+                        mbar_arrive(&sh->kv_empty[vpos % kSlots]);
+                    }
+                    if (j + 1 < it.n_kv) {
+                        if (!(ok = slot_full(kpos))) break;
+                        if (j + 1 < n_x) {
+                            tc_fence_after();
+                            issue_qk(k_desc0 + (kpos % kSlots) * kSlotStep);
+                            tc_commit(&sh->kv_empty[kpos % kSlots]);
+                            if (j + 2 == n_x) tc_commit(&sh->q_empty);  // this tile's last Q.K^T has been issued
+                        } else {
+                            mbar_arrive(&sh->kv_empty[kpos % kSlots]);
+                        }
+                    }
+                }
+                used += n_x > 0 ? 1 : 0;
                 kt += it.n_kv;
             }
         }
@@ -550,20 +565,36 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t t_s = tmem + x * 128 + lane_base;
         const uint32_t t_o = tmem + 256 + x * 128 + lane_base;
         uint32_t tiles = 0;  // tiles finished by this Q tile over all items (barrier phases)
+        // Ping-pong between the two softmax warpgroups.  Both tiles' exponentials go through the same four MUFU
+        // pipes; if both warpgroups exponentiate at once each takes twice as long and afterwards both tiles' MMAs
+        // queue up behind one another.  Inside an item with both tiles active the softmaxes therefore alternate
+        // A(0) B(0) A(1) B(1) ..., so that one tile's MMAs run under the other tile's softmax.
+        uint32_t turns_seen = 0;  // completions of the other tile's turn barrier this warp has consumed
         bool ok = true;
         for (int idx = first_idx; ok && idx < total; idx += stride) {
             const Item it = load_item(p, idx);
             const int n_x = x == 0 ? it.n_a : it.n_b;
             if (n_x == 0) continue;
+            const bool both = it.n_b > 0;
             const int q_pos = it.q0 + x * kTileQ + row;  // position within the sequence
             float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
             for (int j = 0; ok && j < n_x; ++j, ++tiles) {
                 if (!(ok = wait_or_abort(sh, &sh->s_full[x], tiles & 1u))) break;
+                // A(j) starts after B(j-1); B(j) starts after A(j) while A still has tiles.
+                if (both && (x == 0 ? j >= 1 : j < it.n_a)) {
+                    if (!(ok = wait_or_abort(sh, &sh->turn[x ^ 1], turns_seen & 1u))) break;
+                    ++turns_seen;
+                }
                 tc_fence_after();
                 if (j == n_x - 1)
                     ok = softmax_tile<true>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
                 else
                     ok = softmax_tile<false>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+                // hand the turn over: A after each of its tiles, B while A still has a tile that will wait for it
+                if (both && (x == 0 || j + 1 < it.n_a)) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->turn[x]);
+                }
             }
             if (!ok) break;
             // ---- epilogue: O / l -> bf16 -> global, then hand O back to the MMA thread ----
