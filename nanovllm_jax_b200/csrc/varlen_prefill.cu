@@ -19,22 +19,23 @@
 //               128 dims] through one five-slot mbarrier ring filled K0 V0 K1 V1 ...
 //               (cp.async.bulk.tensor, 128-byte swizzle, no multicast): K(j+2) takes the
 //               slot V(j-1) leaves and V(j+2) the slot K(j) leaves, so every tile is
-//               requested about two tiles before it is needed -- the kernel is bound by
-//               the latency of these loads unless that much is in flight.
+//               requested about two tiles before it is needed.
 //   warps 1, 2  MMA issuers, one thread each for Q tile A and Q tile B: S = Q K^T
 //               (operands in shared memory) and O += P V (P read from tensor memory, V
 //               from shared memory, MN-major), M = N = 128, K = 16 per instruction;
 //               tcgen05.commit signals the mbarriers.  Warp 1 also owns the tensor-
 //               memory allocation (512 columns: S_A S_B O_A O_B).
-//   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row
-//               reads its S row from tensor memory (32-column chunks, the next chunk
-//               in flight while the current one is processed), keeps the running
-//               max / sum, writes bf16 P back over S in two halves -- the first half
-//               releases the first four P.V k-steps while the second is still being
-//               exponentiated -- and rescales O only when the max grew by more than
-//               2^8 (exact: the stale max is carried into the final normalisation).
+//   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row holds
+//               its S row (128 scores) in registers, keeps the running max / sum (packed
+//               f32x2 math, 3-input max), writes bf16 P back over S in two halves (each
+//               releases four P.V k-steps) and rescales O only when the max grew by more
+//               than 2^8 (exact: the stale max is carried into the final normalisation).
 //               Tiles strictly above the diagonal are skipped, the diagonal tile is
-//               masked element-wise.
+//               masked element-wise.  The two warpgroups take turns (A(0) B(0) A(1) ...):
+//               they share the four MUFU pipes, and alternating keeps one tile's MMAs
+//               running under the other tile's exponentials.
+// The three measures that only pay off together (each alone hits the next bottleneck at the same
+// level): two MMA issuers, the five-slot ring, and the softmax ping-pong.
 // Every mbarrier wait is bounded; on timeout the CTA raises a device error flag,
 // stops issuing work, and still releases its tensor memory before it exits.
 #include "common.cuh"
