@@ -44,7 +44,7 @@ UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised in profiles/paged_decode_cfg2_qwen3-8b_b64.md and profiles/varlen_prefill_cfg4_qwen3-8b_16seq.md
 # (a property of the launch, independent of the page-pool size the capture used); None where no capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 1_021_617_440, "cfg4": 1_645_496_488}
+NCU_TRAFFIC_BYTES = {"cfg2": 1_021_617_440, "cfg4": 1_380_623_264}
 
 
 def load_peaks():
