@@ -13,6 +13,12 @@ layers/linear.py:497-503), replicated embedding and LM head, sequential page all
 paged decode, varlen prefill -- goes through ``nanovllm_jax_b200.layers.attention.Attention`` with per-rank head
 counts and a per-rank KV-cache shard, exactly as the reference's model would call it (models/qwen3.py:114-120,166).
 
+Status of the numbers: the single-GPU run (CUDA graph replay of the decode step) is measured.  With more than one
+rank the decode step is launched eagerly unless --graph is given: the only multi-rank attempt so far captured the step
+(NCCL all-reduces included) into a CUDA graph on every rank and did not finish, and no GPU time was left to find out
+why (one candidate: a capture that fails on one rank only, which would leave that rank issuing live all-reduces
+against ranks that merely recorded theirs).  Multi-GPU tokens/s are therefore NOT measured yet.
+
 The model is NOT part of the library; it exists so that the attention path can be timed inside a realistic decode
 step.  Weights are N(0, 0.02) random (there is no checkpoint in the image), prompts are uniform random token ids.
 Prints one JSON line on rank 0.
@@ -240,6 +246,7 @@ def main():
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--graph", action="store_true", help="with more than one rank: capture the decode step anyway")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -262,7 +269,8 @@ def main():
     first = eng.prefill()
     torch.cuda.synchronize()
     t_prefill = time.perf_counter() - t0
-    tokens, t_decode = eng.decode(first, use_graph=not args.no_graph)
+    use_graph = (not args.no_graph) and (world == 1 or args.graph)
+    tokens, t_decode = eng.decode(first, use_graph=use_graph)
     if world > 1:
         t = torch.tensor([t_prefill, t_decode], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
