@@ -168,7 +168,8 @@ size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KV
  *                 cu_seqlens_host is NULL)
  *
  * Unlike the reference, rows beyond the 8192-token bucket (utils/context.py:18-32)
- * are computed rather than returned as zeros.
+ * are computed rather than returned as zeros.  Rows of `out` at token indices
+ * >= cu_seqlens_q[B] belong to no sequence and are left untouched.
  */
 int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v,
                               const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,

@@ -139,6 +139,9 @@ def varlen_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens
         if keep.shape[0] != b + 1:
             raise ValueError("cu_seqlens_host length mismatch")
         host_ptr = keep.data_ptr()
+        covered = int(keep[-1])
+        if 0 <= covered < t:
+            out[covered:].zero_()  # rows that belong to no sequence: the reference returns zeros there (:272-277)
     with torch.cuda.device(q.device):
         lib = _lib.load()
         need = int(lib.nvllm_b200_varlen_prefill_workspace_bytes(t, b, h, kvh, d))
