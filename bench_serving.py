@@ -216,13 +216,22 @@ class Engine:
             self.d_ids.copy_(first_tokens)
             try:
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                # thread_local: the NCCL watchdog thread may touch CUDA while this thread captures
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     self._decode_step_device()
                 self.graph = g
             except Exception as exc:  # capture unsupported here: run the step eagerly and say so
                 self.graph = None
                 self.graph_error = f"{type(exc).__name__}: {exc}"[:200]
                 torch.cuda.synchronize()
+            if self.m.tp > 1:
+                # Every rank must take the same path: a rank replaying a graph never meets a rank that issues its
+                # all-reduces live.  One failed capture sends everybody to the eager step.
+                agreed = torch.tensor([1 if self.graph is not None else 0], device=self.m.dev)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+                if int(agreed.item()) == 0:
+                    self.graph = None
+                    self.graph_error = self.graph_error or "capture failed on another rank"
             self.d_ids.copy_(first_tokens)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
