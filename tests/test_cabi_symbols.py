@@ -94,3 +94,21 @@ def test_operators_reject_host_tensors():
         ops.paged_decode(x, x, x, x, x, 0.1, 256)
     with pytest.raises(TypeError):
         ops.store_kvcache(x, x, x, x, torch.zeros(2, dtype=torch.int32))
+
+
+def test_jax_glue_imports_without_jax_and_names_its_targets():
+    """The jax.ffi module is shipped but cannot run here: it must import cleanly, say why it cannot be used, and the
+    adapter source must define exactly the handlers it registers, each forwarding to a declared C-ABI entry point."""
+    from nanovllm_jax_b200 import jax_ffi
+    assert os.path.isfile(jax_ffi.ADAPTER_SOURCE)
+    src = open(jax_ffi.ADAPTER_SOURCE).read()
+    for name in jax_ffi.TARGETS:
+        assert f"XLA_FFI_DEFINE_HANDLER_SYMBOL({name}," in src
+    declared = set(_declared())
+    for call in ("nvllm_b200_store_kvcache", "nvllm_b200_paged_decode", "nvllm_b200_varlen_prefill"):
+        assert call in declared and call + "(" in src
+    try:
+        import jax  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError, match="JAX"):
+            jax_ffi.paged_attention(None, None, None, None, None, 0.1, 256)
