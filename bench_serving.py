@@ -247,6 +247,15 @@ class Engine:
         return out, time.perf_counter() - t0
 
 
+def _stage(msg: str) -> None:
+    """Progress marker on stderr (NVLLM_SERVING_VERBOSE=1): shows how far each rank got if a run stalls."""
+    if os.environ.get("NVLLM_SERVING_VERBOSE", "0") == "1":
+        print(f"[rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:7.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
+_T0 = time.perf_counter()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -264,22 +273,29 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    _stage("start")
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        _stage("process group up")
     cfg = Qwen3Config(layers=args.layers)
     model = Qwen3(cfg, world, rank, dev)
+    _stage("weights drawn")
     rng = np.random.Generator(np.random.PCG64(5000))
     prompts = rng.integers(0, cfg.vocab, size=(args.requests, args.prompt_len))
     eng = Engine(model, prompts, args.gen_len)
     torch.cuda.synchronize()
+    _stage("cache allocated")
     if world > 1:
         dist.barrier()
+        _stage("barrier passed")
     t0 = time.perf_counter()
     first = eng.prefill()
     torch.cuda.synchronize()
     t_prefill = time.perf_counter() - t0
+    _stage(f"prefill done in {t_prefill:.2f}s")
     use_graph = (not args.no_graph) and (world == 1 or args.graph)
     tokens, t_decode = eng.decode(first, use_graph=use_graph)
+    _stage(f"decode done in {t_decode:.2f}s")
     if world > 1:
         t = torch.tensor([t_prefill, t_decode], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
