@@ -112,3 +112,33 @@ def test_jax_glue_imports_without_jax_and_names_its_targets():
     except ImportError:
         with pytest.raises(ImportError, match="JAX"):
             jax_ffi.paged_attention(None, None, None, None, None, 0.1, 256)
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(lib, tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 with no C++ or torch types, and a C program linked
+    against the shared library must be able to call it (argument validation only: no GPU needed)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    from nanovllm_jax_b200 import _lib
+    src = tmp_path / "host.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "nvllm_b200_attn.h"\n'
+        "int main(void) {\n"
+        "    if (nvllm_b200_version() <= 0) return 1;\n"
+        "    /* head_dim 64 is outside the supported set: must answer with a code and a message, not crash */\n"
+        "    int rc = nvllm_b200_store_kvcache(0, 0, 0, 0, 0, 4, 8, 64, 1024, 0, 0);\n"
+        '    printf("%d %s\\n", rc, nvllm_b200_last_error_string());\n'
+        "    return rc < 0 ? 0 : 2;\n"
+        "}\n")
+    exe = tmp_path / "host"
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe), "-L", libdir, "-l:libnvllm_b200_attn.so", f"-Wl,-rpath,{libdir}"],
+                   check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stdout + out.stderr
+    code, _, text = out.stdout.strip().partition(" ")
+    assert int(code) < 0 and len(text) > 0
