@@ -10,7 +10,8 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnvllm_b200_attn.so")
+# NVLLM_B200_LIB points the package at another build of the same library (e.g. a candidate kernel under test).
+LIB_PATH = os.environ.get("NVLLM_B200_LIB") or os.path.join(_HERE, "libnvllm_b200_attn.so")
 
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDRIVER = 0, -1, -2, -3, -4, -5
 DTYPE_BF16, DTYPE_F32 = 0, 1
