@@ -8,7 +8,9 @@ import os
 
 import pytest
 
-REF = os.environ.get("NANOVLLM_JAX_REFERENCE", "/root/reference")
+# the reference checkout: NANOVLLM_JAX_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("NANOVLLM_JAX_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isfile(os.path.join(REF, "layers", "attention.py")),
                                 reason="reference checkout not available")
 
