@@ -380,7 +380,10 @@ def run_b200(args):
         t_end.record()
         torch.cuda.synchronize()
     elapsed_ms = t_start.elapsed_time(t_end)
-    decode_ms = float(np.mean([a.elapsed_time(b) for a, b in zip(ev_a, ev_b)])) if n_ev else float("nan")
+    decode_samples = [a.elapsed_time(b) for a, b in zip(ev_a, ev_b)]
+    decode_ms = float(np.mean(decode_samples)) if n_ev else float("nan")
+    # spread of the kernel-only samples on this rank: [p10, median, p90] in microseconds
+    decode_pct = [float(x) * 1e3 for x in np.percentile(decode_samples, [10, 50, 90])] if n_ev else None
     if world > 1:
         t = torch.tensor([elapsed_ms, decode_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -428,6 +431,7 @@ def run_b200(args):
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "kernel": "paged_decode_kernel + paged_decode_merge_kernel (one C-ABI call)",
                          "bytes_per_launch": decode_bytes, "us_per_launch": decode_ms * 1e3,
+                         "us_per_launch_p10_p50_p90": decode_pct, "launches_timed": n_ev,
                          "peak_kind": f"{peak_kind} copy bandwidth", "frac_of_nominal_8tbs": achieved / 8000.0},
             "e2e": {"value": world * step_bytes / (e2e_ms / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
