@@ -56,3 +56,31 @@ def test_page_sets_are_disjoint_and_bytes_add_up():
     ctx = int(w.context_lens.astype(np.int64).sum())
     assert w.kv_bytes() == ctx * 8 * 128 * 4 + 2 * 64 * 32 * 128 * 2 + 4 * (sum(len(b) for b in w.block_lists) + 64)
     assert w.kv_bytes(4) < w.kv_bytes() and workloads.config4().flops() > 9e11
+
+
+def test_step_inputs_are_views_of_one_buffer_and_one_copy_moves_them_all():
+    """The end-to-end step moves q, k, v and the index tensors with ONE host -> device copy: every device tensor must
+    alias the device buffer, keep its dtype / shape / contiguity, and change when the flat buffer is overwritten."""
+    import torch
+    sys.path.insert(0, ROOT)
+    import bench
+    w = bench.pick_workload("cfg1", None)
+    sets = bench.page_sets(w)
+    host, devflat, devin = bench.make_step_inputs(w, sets, 16, 8, "cpu", pin=False)
+    assert len(host) == len(devflat) == len(devin) == len(sets)
+    for (tables, slots), hflat, dflat, views in zip(sets, host, devflat, devin):
+        q, k, v, sl, cl, bt = views
+        assert q.shape == (w.batch, 16, w.head_dim) and q.dtype == torch.bfloat16 and q.is_contiguous()
+        assert k.shape == v.shape == (w.batch, 8, w.head_dim)
+        assert sl.dtype == cl.dtype == bt.dtype == torch.int32
+        assert np.array_equal(sl.numpy(), slots) and np.array_equal(bt.numpy(), tables)
+        assert np.array_equal(cl.numpy(), w.context_lens.astype(np.int32))
+        lo, hi = dflat.data_ptr(), dflat.data_ptr() + dflat.numel()
+        for t in views:
+            assert lo <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= hi
+            assert (t.data_ptr() - lo) % 256 == 0
+        assert torch.equal(dflat, hflat)
+        before = q.clone()
+        hflat.zero_()
+        dflat.copy_(hflat)  # the single copy of the end-to-end step
+        assert not torch.equal(q, before) and int(sl.abs().sum()) == 0 and int(bt.abs().sum()) == 0
