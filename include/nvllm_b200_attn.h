@@ -77,8 +77,9 @@ int nvllm_b200_store_kvcache(const void* k, const void* v, void* k_cache, void* 
                              int64_t num_slots, int src_dtype, void* stream);
 
 /*
- * Bytes of scratch nvllm_b200_paged_decode needs for these sizes (always > 0,
- * a multiple of 256).  Depends only on (H, D) and the device's SM count.
+ * Bytes of scratch nvllm_b200_paged_decode / nvllm_b200_decode_step need for
+ * these sizes (always > 0, a multiple of 256).  Depends on B, KVH, H/KVH and the
+ * current device's SM count.
  */
 size_t nvllm_b200_paged_decode_workspace_bytes(int B, int H, int KVH, int D, int MB, int block_size);
 
@@ -109,6 +110,22 @@ int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_ca
                             float scale, void* stream);
 
 /*
+ * decode_step: what Attention.__call__ does for one layer in the decode phase
+ * (layers/attention.py:436-480, decode branch): scatter the step's new K/V rows
+ * into the cache by slot (store_kv_to_cache, :465-467), then attend over the
+ * pages (_decode_attention, :366-397) -- one C call, two kernel launches.
+ * Equivalent to nvllm_b200_store_kvcache(k, v, ..., T = B) followed by
+ * nvllm_b200_paged_decode(...) on the same stream, with the same argument
+ * meanings, limits and workspace size; k and v are [B, KVH, D] in src_dtype.
+ */
+int nvllm_b200_decode_step(const void* q, const void* k, const void* v, void* k_cache, void* v_cache,
+                           const int32_t* slot_mapping, const int32_t* block_tables,
+                           const int32_t* context_lens, void* out,
+                           void* workspace, size_t workspace_bytes,
+                           int B, int H, int KVH, int D, int NB, int block_size, int MB,
+                           float scale, int src_dtype, void* stream);
+
+/*
  * paged_decode_static: the same computation as nvllm_b200_paged_decode, for callers that can give the
  * library no scratch buffer and cannot allocate one themselves.  It has no counterpart in the reference.
  *
@@ -117,22 +134,22 @@ int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_ca
  * in a process whose memory pool already owns almost all of HBM, so that a cudaMalloc may fail or take
  * memory the pool counts on, or a latency-critical loop that must avoid the device-wide synchronisation
  * cudaMalloc and cudaFree cause.  This entry point calls no allocating routine: its split-K scratch is a
- * fixed array of about 2.7 MB inside the library image, present on every device that loads the library
+ * fixed array of about 2.8 MB inside the library image, present on every device that loads the library
  * for as long as the process lives.
  *
- * Limits (beyond those of nvllm_b200_paged_decode): B <= 4096 sequences, and a device with at most
- * 160 SMs (the main kernel runs 2 CTAs per SM and the array holds the partial results of 320).  Larger
+ * Limits (beyond those of nvllm_b200_paged_decode): B <= 4096 sequences and B * KVH <= 32768, and a
+ * device with at most 160 SMs (the main kernel runs 2 CTAs per SM and the array holds the partial results of 320).  Larger
  * sizes return NVLLM_B200_EWORKSPACE and the error text names the limit; nothing is launched.
  *
  * The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
  * device current, which may also make the runtime load the library's device code); make that first call
  * outside any stream capture.  Later calls only enqueue kernels on `stream`.
  *
- * All calls on a device share the one array, and it keeps whatever the previous call left in it.  Nothing
- * in it needs to be zero at the start of a call (every word a call reads it has written earlier in the
- * same call), so there is nothing to clear between calls; but two calls whose kernels may overlap on the
- * GPU -- different streams, or different host threads without ordering -- race on it and corrupt each
- * other's results.  Issue them on one stream, or order them with events.
+ * All calls on a device share the one array, and it keeps whatever the previous call left in it.  The
+ * words that must start at zero (one arrival counter per sequence and kv head) are cleared by the call's
+ * own first kernel, so there is nothing for the caller to clear between calls; but two calls whose
+ * kernels may overlap on the GPU -- different streams, or different host threads without ordering -- race
+ * on it and corrupt each other's results.  Issue them on one stream, or order them with events.
  */
 int nvllm_b200_paged_decode_static(const void* q, const void* k_cache, const void* v_cache,
                                    const int32_t* block_tables, const int32_t* context_lens, void* out,

@@ -26,6 +26,7 @@ SIGNATURES = {
     "nvllm_b200_store_kvcache": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i32, _vp]),
     "nvllm_b200_paged_decode_workspace_bytes": (_sz, [_i32] * 6),
     "nvllm_b200_paged_decode": (_i32, [_vp] * 7 + [_sz] + [_i32] * 7 + [_f32, _vp]),
+    "nvllm_b200_decode_step": (_i32, [_vp] * 10 + [_sz] + [_i32] * 7 + [_f32, _i32, _vp]),
     "nvllm_b200_paged_decode_static": (_i32, [_vp] * 6 + [_i32] * 7 + [_f32, _vp]),
     "nvllm_b200_device_status": (_i32, [_c.POINTER(_i32)]),
     "nvllm_b200_varlen_prefill_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),

@@ -21,15 +21,21 @@
 //    q.K^T and P.V; the online softmax (exp2 domain) lives in registers with
 //    warp-shuffle row reductions.
 //  * A range that ends inside a sequence leaves an fp32 partial (m, l, O) in
-//    the caller's workspace; a second, tiny kernel merges the partials of split
-//    sequences.  Sequences wholly inside one range are written directly.
+//    the caller's workspace and takes a ticket for that (sequence, kv head); the
+//    CTA that draws the last ticket combines all partials of the sequence, in
+//    group order (bitwise reproducible whichever CTA arrives last), and writes
+//    the rows.  Nobody waits for anybody.  Sequences wholly inside one range are
+//    written directly.  The tickets are cleared by the small kernel that runs
+//    before this one (decode_prepare_kernel, which in the fused decode step
+//    also scatters the step's new K/V rows into the cache).
 //
 // No spin-wait is unbounded: every mbarrier wait gives up after a poll limit,
 // raises a device error flag (readable through nvllm_b200_device_status) and
 // the CTA drains and returns.
-#include "common.cuh"
+#include "store_kvcache.cuh"
 
 #include <mutex>
+#include <string.h>
 
 namespace nvllm {
 namespace decode {
@@ -60,8 +66,8 @@ struct Params {
     const int32_t* block_tables;
     const int32_t* context_lens;
     __nv_bfloat16* out;
-    float* partials;   // [grid][2][partial_floats]
-    int32_t* prefix;   // [B+1] exclusive prefix of tiles per sequence, last = total
+    float* partials;        // [grid][2][partial_floats]
+    unsigned int* tickets;  // [B*KVH] partials delivered so far per (sequence, kv head); zero when the kernel starts
     int B, H, KVH, G, NB, block_size, MB;
     int num_groups;
     float scale_log2;
@@ -113,6 +119,47 @@ __device__ __forceinline__ int next_item(Walk& w, const Params& p, int max_ctx, 
     return 0;
 }
 
+// Combine the partials of sequence b (tiles [first, first + tb) of the per-head tile stream) for kv head kvh and
+// write its G output rows; thread d of the 128 callers owns output dim d.  Partials are read in group order and
+// four at a time, so the result does not depend on which CTA runs this.
+__device__ __forceinline__ void merge_sequence(const Params& p, int b, int kvh, long long first, int tb,
+                                               long long total, int d) {
+    const int ng = p.num_groups;
+    long long gf = ((first + 1) * ng - 1) / total;
+    long long gl = ((first + tb) * ng - 1) / total;
+    if (gf > ng - 1) gf = ng - 1;
+    if (gl > ng - 1) gl = ng - 1;
+    const size_t pf = partial_floats(p.G);
+    for (int r = 0; r < p.G; ++r) {
+        float mt = -INFINITY, acc = 0.f, lt = 0.f;
+        for (long long g0 = gf; g0 <= gl; g0 += 4) {
+            float mv[4], lv[4], ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long g = g0 + u;
+                const bool live = g <= gl && (g * total / ng < (g + 1) * total / ng);  // skip empty groups
+                const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf;
+                mv[u] = live ? __ldcg(part + p.G * kD + r) : -INFINITY;
+                lv[u] = live ? __ldcg(part + p.G * kD + kMaxG + r) : 0.f;
+                ov[u] = live ? __ldcg(part + r * kD + d) : 0.f;
+            }
+            const float mnew = fmaxf(fmaxf(mt, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+            if (mnew == -INFINITY) continue;
+            const float sc = (mt == -INFINITY) ? 0.f : fast_exp2(mt - mnew);
+            acc *= sc;
+            lt *= sc;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float f = (mv[u] == -INFINITY) ? 0.f : fast_exp2(mv[u] - mnew);
+                acc += ov[u] * f;
+                lt += lv[u] * f;
+            }
+            mt = mnew;
+        }
+        p.out[((size_t)b * p.H + (size_t)kvh * p.G + r) * kD + d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const Params p) {
@@ -148,13 +195,23 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     // Programmatic dependent launch: everything above overlapped the tail of the previous kernel in the
     // stream; nothing below may touch global memory before that kernel's writes are visible.
     griddep_wait();
-    griddep_launch_dependents();  // lets the merge kernel's launch proceed while this grid streams
+    griddep_launch_dependents();  // lets the next kernel of the stream run its own prologue while this grid streams
 
     // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
+    // Every CTA scans context_lens itself (B / 160 values per thread and one warp scan): that is one global
+    // load latency, paid in parallel by all CTAs, and cheaper than fetching the result of a serial plan.
     const int per = (p.B + kThreads - 1) / kThreads;
     const int b_lo = min(p.B, tid * per), b_hi = min(p.B, b_lo + per);
     int mine = 0;
-    for (int b = b_lo; b < b_hi; ++b) mine += tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
+    for (int b = b_lo; b < b_hi; ++b) {
+        const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
+        mine += tb;
+        if (tb == 0 && b % p.num_groups == group) {
+            // an empty sequence attends to nothing: its rows are zeros (one CTA per kv head writes them)
+            uint4* orow = reinterpret_cast<uint4*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G) * kD);
+            for (int i = 0; i < p.G * (kD * 2 / 16); ++i) orow[i] = make_uint4(0, 0, 0, 0);
+        }
+    }
     int incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -171,20 +228,18 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (w < warp) warp_off += v;
         total += v;
     }
-    const long long x0 = group < p.num_groups ? (long long)group * total / p.num_groups : total;
-    const long long x1 = group < p.num_groups ? (long long)(group + 1) * total / p.num_groups : total;
+    const long long x0 = (long long)group * total / p.num_groups;
+    const long long x1 = (long long)(group + 1) * total / p.num_groups;
     {
         long long run = warp_off + incl - mine;
         for (int b = b_lo; b < b_hi; ++b) {
             const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
-            if (blockIdx.x == 0) p.prefix[b] = (int)run;
             if (tb > 0 && run <= x0 && x0 < run + tb) {
                 sm_i[10] = b;
                 sm_i[11] = (int)(x0 - run);
             }
             run += tb;
         }
-        if (blockIdx.x == 0 && tid == 0) p.prefix[p.B] = (int)total;
     }
     __syncthreads();
     if (x0 >= x1 || sm_i[10] < 0) return;  // nothing to do (uniform across the CTA)
@@ -411,6 +466,22 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     }
                 }
             }
+            if (!full_item) {
+                // Publish the partial, then take a ticket for this (sequence, kv head).  Whoever draws the last
+                // ticket finds every partial of the sequence visible and combines them; nobody waits.
+                __threadfence();
+                named_barrier_sync(1, kConsumerWarps * 32);
+                if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
+                named_barrier_sync(1, kConsumerWarps * 32);
+                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
+                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
+                if (total >= p.num_groups)
+                    parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
+                if ((long long)sm_i[9] == parts - 1) {
+                    __threadfence();
+                    merge_sequence(p, walk.b, kvh, first, tb, total, ctid);
+                }
+            }
         }
         walk.left -= n;
         walk.t += n;
@@ -421,56 +492,23 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     }
 }
 
-// One CTA per (sequence, kv head, query head of the group), one thread per output dim: combine the
-// partials of a sequence whose tiles were cut across groups (fixed order, so bitwise reproducible);
-// write a zero row for an empty sequence; leave every other row alone.
-__global__ void __launch_bounds__(kD) paged_decode_merge_kernel(const Params p) {
-    griddep_wait();  // partials, prefix and out rows of the main kernel must be complete and visible
-    const int r = blockIdx.x % p.G;
-    const int kvh = (blockIdx.x / p.G) % p.KVH;
-    const int b = blockIdx.x / (p.G * p.KVH);
-    const int d = threadIdx.x;
-    const long long total = p.prefix[p.B];
-    const long long first = p.prefix[b];
-    const long long tb = p.prefix[b + 1] - first;
-    __nv_bfloat16* orow = p.out + ((size_t)b * p.H + (size_t)kvh * p.G + r) * kD;
-    if (tb == 0) {
-        orow[d] = __float2bfloat16_rn(0.f);
-        return;
+// Clears the tickets of one decode call and, in the fused decode step, scatters the step's new K/V rows into
+// the cache (blocks [0, store_blocks) do the scatter, the rest clear).  Runs right before paged_decode_kernel
+// on the same stream.
+template <typename SrcT>
+__global__ void __launch_bounds__(kStoreThreads)
+decode_prepare_kernel(unsigned int* __restrict__ tickets, int num_tickets, int store_blocks,
+                      const SrcT* __restrict__ k, const SrcT* __restrict__ v, __nv_bfloat16* __restrict__ k_cache,
+                      __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping,
+                      int64_t total_chunks, int row_chunks, int64_t num_slots) {
+    griddep_wait();  // the previous kernel may still be reading these tickets or the cache rows written below
+    griddep_launch_dependents();
+    if ((int)blockIdx.x < store_blocks) {
+        store_block<SrcT>(blockIdx.x, k, v, k_cache, v_cache, slot_mapping, total_chunks, row_chunks, num_slots);
+    } else {
+        const int i = ((int)blockIdx.x - store_blocks) * kStoreThreads + threadIdx.x;
+        if (i < num_tickets) tickets[i] = 0u;
     }
-    const int ng = p.num_groups;
-    long long gf = ((first + 1) * ng - 1) / total;
-    long long gl = ((first + tb) * ng - 1) / total;
-    if (gf > ng - 1) gf = ng - 1;
-    if (gl > ng - 1) gl = ng - 1;
-    if (gf == gl) return;
-    const size_t pf = partial_floats(p.G);
-    float mt = -INFINITY, acc = 0.f, lt = 0.f;
-    for (long long g0 = gf; g0 <= gl; g0 += 4) {
-        float mv[4], lv[4], ov[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const long long g = g0 + u;
-            const bool live = g <= gl && (g * total / ng < (g + 1) * total / ng);  // skip empty groups
-            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf;
-            mv[u] = live ? part[p.G * kD + r] : -INFINITY;
-            lv[u] = live ? part[p.G * kD + kMaxG + r] : 0.f;
-            ov[u] = live ? part[r * kD + d] : 0.f;
-        }
-        const float mnew = fmaxf(fmaxf(mt, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
-        if (mnew == -INFINITY) continue;
-        const float sc = (mt == -INFINITY) ? 0.f : fast_exp2(mt - mnew);
-        acc *= sc;
-        lt *= sc;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const float f = (mv[u] == -INFINITY) ? 0.f : fast_exp2(mv[u] - mnew);
-            acc += ov[u] * f;
-            lt += lv[u] * f;
-        }
-        mt = mnew;
-    }
-    orow[d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
 }
 
 // ---------------------------------------------------------------------------
@@ -480,7 +518,35 @@ static int main_grid() { return kCtasPerSm * sm_count(); }
 
 static size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 
-static int make_cache_map(CUtensorMap* map, const void* base, int64_t num_slots, int KVH) {
+static size_t ticket_bytes(int B, int KVH) { return round256((size_t)B * KVH * 4); }
+static size_t partial_bytes(int ctas, int G) { return round256((size_t)ctas * 2 * partial_floats(G) * 4); }
+
+// Tensor maps of the caches seen so far, keyed by what they encode (base address, slots, kv heads).  Encoding
+// one costs the host a microsecond or two per call; a serving loop hands over the same few caches for ever.
+// A map holds no reference to the memory: an entry stays valid for any later buffer with the same key.
+static int cached_cache_map(CUtensorMap* map, const void* base, int64_t num_slots, int KVH) {
+    struct Entry {
+        const void* base;
+        int64_t num_slots;
+        int kvh, dev;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 256;  // two per layer of a 128-layer model
+    static std::mutex mu;
+    static Entry table[kEntries];
+    static int used = 0, next = 0;
+    int dev = 0;
+    NVLLM_CUDA_OK(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < used; ++i) {
+            const Entry& e = table[i];
+            if (e.base == base && e.num_slots == num_slots && e.kvh == KVH && e.dev == dev) {
+                memcpy(map, &e.map, sizeof(CUtensorMap));
+                return NVLLM_B200_OK;
+            }
+        }
+    }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled entry point not available");
     cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)KVH, (cuuint64_t)num_slots};
@@ -491,6 +557,13 @@ static int make_cache_map(CUtensorMap* map, const void* base, int64_t num_slots,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(NVLLM_B200_EDRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    std::lock_guard<std::mutex> lock(mu);
+    Entry& e = table[used < kEntries ? used++ : (next = (next + 1) % kEntries)];
+    e.base = base;
+    e.num_slots = num_slots;
+    e.kvh = KVH;
+    e.dev = dev;
+    memcpy(&e.map, map, sizeof(CUtensorMap));
     return NVLLM_B200_OK;
 }
 
@@ -507,6 +580,133 @@ static int ensure_smem_attr() {
     return NVLLM_B200_OK;
 }
 
+// What every decode entry point shares: the argument checks and the two launches.  `tickets` / `partials` point
+// into whatever scratch the entry point owns; `step` (may be null) adds the scatter of the step's new K/V rows
+// to the first launch.
+struct DecodeArgs {
+    const void *q, *k_cache, *v_cache;
+    const int32_t *block_tables, *context_lens;
+    void* out;
+    int B, H, KVH, D, NB, block_size, MB;
+    float scale;
+    void* stream;
+};
+struct StepArgs {
+    const void *k, *v;
+    const int32_t* slot_mapping;
+    int src_dtype;
+};
+
+static int check_decode_args(const char* who, const DecodeArgs& a) {
+    if (a.B < 0 || a.H <= 0 || a.KVH <= 0 || a.NB <= 0 || a.block_size <= 0 || a.MB <= 0)
+        return fail(NVLLM_B200_EINVAL, "%s: non-positive size (B=%d H=%d KVH=%d NB=%d block=%d MB=%d)", who, a.B, a.H,
+                    a.KVH, a.NB, a.block_size, a.MB);
+    if (a.D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "%s: head_dim %d (only 128)", who, a.D);
+    if (a.block_size % kTile != 0)
+        return fail(NVLLM_B200_EUNSUPPORTED, "%s: block_size %d must be a multiple of %d", who, a.block_size, kTile);
+    if (a.H % a.KVH != 0 || a.H / a.KVH > kMaxG)
+        return fail(NVLLM_B200_EUNSUPPORTED, "%s: H/KVH = %d/%d must be an integer <= %d", who, a.H, a.KVH, kMaxG);
+    if ((long long)a.MB * a.block_size > 0x3fffffffLL || (long long)a.NB * a.block_size > 0x7fffffffLL)
+        return fail(NVLLM_B200_EUNSUPPORTED, "%s: cache or context too large for 32-bit token indices", who);
+    if ((long long)a.B * a.KVH > 0x3fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "%s: batch too large", who);
+    return NVLLM_B200_OK;
+}
+
+static int check_decode_pointers(const char* who, const DecodeArgs& a) {
+    if (!a.q || !a.k_cache || !a.v_cache || !a.block_tables || !a.context_lens || !a.out)
+        return fail(NVLLM_B200_EINVAL, "%s: null pointer", who);
+    if (((uintptr_t)a.q | (uintptr_t)a.k_cache | (uintptr_t)a.v_cache | (uintptr_t)a.out) & 15)
+        return fail(NVLLM_B200_EINVAL, "%s: q/k_cache/v_cache/out must be 16-byte aligned", who);
+    if (a.KVH > main_grid())
+        return fail(NVLLM_B200_EUNSUPPORTED, "%s: KVH %d exceeds the CTA count %d", who, a.KVH, main_grid());
+    return NVLLM_B200_OK;
+}
+
+static int launch_decode(const char* who, const DecodeArgs& a, const StepArgs* step, unsigned int* tickets,
+                         float* partials) {
+    int rc = ensure_smem_attr();
+    if (rc) return rc;
+    CUtensorMap tm_k, tm_v;
+    const int64_t num_slots = (int64_t)a.NB * a.block_size;
+    if ((rc = cached_cache_map(&tm_k, a.k_cache, num_slots, a.KVH))) return rc;
+    if ((rc = cached_cache_map(&tm_v, a.v_cache, num_slots, a.KVH))) return rc;
+
+    Params p;
+    p.q = (const __nv_bfloat16*)a.q;
+    p.block_tables = a.block_tables;
+    p.context_lens = a.context_lens;
+    p.out = (__nv_bfloat16*)a.out;
+    p.tickets = tickets;
+    p.partials = partials;
+    p.B = a.B;
+    p.H = a.H;
+    p.KVH = a.KVH;
+    p.G = a.H / a.KVH;
+    p.NB = a.NB;
+    p.block_size = a.block_size;
+    p.MB = a.MB;
+    p.num_groups = main_grid() / a.KVH;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+
+    const int num_tickets = a.B * a.KVH;
+    const int clear_blocks = (num_tickets + kStoreThreads - 1) / kStoreThreads;
+    const int row_chunks = a.KVH * kD / 8;
+    const int64_t total_chunks = step ? (int64_t)a.B * row_chunks : 0;
+    const int64_t store_blocks = step ? store_blocks_for(total_chunks) : 0;
+    if (store_blocks + clear_blocks > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "%s: batch too large", who);
+    cfg.gridDim = dim3((unsigned)(store_blocks + clear_blocks));
+    cfg.blockDim = dim3(kStoreThreads);
+    cfg.dynamicSmemBytes = 0;
+    if (step && step->src_dtype == NVLLM_B200_DTYPE_F32) {
+        NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_prepare_kernel<float>, tickets, num_tickets, (int)store_blocks,
+                                         (const float*)step->k, (const float*)step->v, (__nv_bfloat16*)a.k_cache,
+                                         (__nv_bfloat16*)a.v_cache, step->slot_mapping, total_chunks, row_chunks,
+                                         num_slots));
+    } else {
+        NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_prepare_kernel<__nv_bfloat16>, tickets, num_tickets,
+                                         (int)store_blocks, (const __nv_bfloat16*)(step ? step->k : nullptr),
+                                         (const __nv_bfloat16*)(step ? step->v : nullptr), (__nv_bfloat16*)a.k_cache,
+                                         (__nv_bfloat16*)a.v_cache, step ? step->slot_mapping : nullptr, total_chunks,
+                                         row_chunks, num_slots));
+    }
+    cfg.gridDim = dim3((unsigned)(p.num_groups * a.KVH));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_kernel, tm_k, tm_v, p));
+    return NVLLM_B200_OK;
+}
+
+static int decode_with_workspace(const char* who, const DecodeArgs& a, const StepArgs* step, void* workspace,
+                                 size_t workspace_bytes) {
+    int rc = check_decode_args(who, a);
+    if (rc) return rc;
+    if (step) {
+        if (step->src_dtype != NVLLM_B200_DTYPE_BF16 && step->src_dtype != NVLLM_B200_DTYPE_F32)
+            return fail(NVLLM_B200_EUNSUPPORTED, "%s: src_dtype %d", who, step->src_dtype);
+    }
+    if (a.B == 0) return NVLLM_B200_OK;
+    if ((rc = check_decode_pointers(who, a))) return rc;
+    if (step) {
+        if (!step->k || !step->v || !step->slot_mapping) return fail(NVLLM_B200_EINVAL, "%s: null pointer", who);
+        if (((uintptr_t)step->k | (uintptr_t)step->v) & 15)
+            return fail(NVLLM_B200_EINVAL, "%s: k/v must be 16-byte aligned", who);
+    }
+    const size_t need = nvllm_b200_paged_decode_workspace_bytes(a.B, a.H, a.KVH, a.D, a.MB, a.block_size);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))
+        return fail(NVLLM_B200_EWORKSPACE, "%s: workspace of %zu bytes (256-byte aligned) required, got %zu", who, need,
+                    workspace ? workspace_bytes : (size_t)0);
+    return launch_decode(who, a, step, (unsigned int*)workspace,
+                         (float*)((uint8_t*)workspace + ticket_bytes(a.B, a.KVH)));
+}
+
 }  // namespace decode
 }  // namespace nvllm
 
@@ -516,78 +716,29 @@ extern "C" size_t nvllm_b200_paged_decode_workspace_bytes(int B, int H, int KVH,
     (void)MB;
     (void)block_size;
     if (B < 0 || H <= 0 || KVH <= 0 || H % KVH != 0) return 256;
-    const int G = H / KVH;
-    return round256((size_t)(B + 1) * 4) + round256((size_t)main_grid() * 2 * partial_floats(G) * 4) + 256;
+    return ticket_bytes(B, KVH) + partial_bytes(main_grid(), H / KVH) + 256;
 }
 
 extern "C" int nvllm_b200_paged_decode(const void* q, const void* k_cache, const void* v_cache,
                                        const int32_t* block_tables, const int32_t* context_lens, void* out,
                                        void* workspace, size_t workspace_bytes, int B, int H, int KVH, int D, int NB,
                                        int block_size, int MB, float scale, void* stream) {
-    using namespace nvllm;
     using namespace nvllm::decode;
-    if (B < 0 || H <= 0 || KVH <= 0 || NB <= 0 || block_size <= 0 || MB <= 0)
-        return fail(NVLLM_B200_EINVAL, "paged_decode: non-positive size (B=%d H=%d KVH=%d NB=%d block=%d MB=%d)", B, H,
-                    KVH, NB, block_size, MB);
-    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: head_dim %d (only 128)", D);
-    if (block_size % kTile != 0)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: block_size %d must be a multiple of %d", block_size, kTile);
-    if (H % KVH != 0 || H / KVH > kMaxG)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: H/KVH = %d/%d must be an integer <= %d", H, KVH, kMaxG);
-    if ((long long)MB * block_size > 0x3fffffffLL || (long long)NB * block_size > 0x7fffffffLL)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: cache or context too large for 32-bit token indices");
-    if (B == 0) return NVLLM_B200_OK;
-    if (!q || !k_cache || !v_cache || !block_tables || !context_lens || !out)
-        return fail(NVLLM_B200_EINVAL, "paged_decode: null pointer");
-    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
-        return fail(NVLLM_B200_EINVAL, "paged_decode: q/k_cache/v_cache/out must be 16-byte aligned");
-    const size_t need = nvllm_b200_paged_decode_workspace_bytes(B, H, KVH, D, MB, block_size);
-    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))
-        return fail(NVLLM_B200_EWORKSPACE, "paged_decode: workspace of %zu bytes (256-byte aligned) required, got %zu",
-                    need, workspace ? workspace_bytes : (size_t)0);
-    const int grid = main_grid();
-    if (KVH > grid) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode: KVH %d exceeds the CTA count %d", KVH, grid);
-    int rc = ensure_smem_attr();
-    if (rc) return rc;
+    const DecodeArgs a = {q, k_cache, v_cache, block_tables, context_lens, out, B, H, KVH, D, NB, block_size, MB, scale,
+                          stream};
+    return decode_with_workspace("paged_decode", a, nullptr, workspace, workspace_bytes);
+}
 
-    CUtensorMap tm_k, tm_v;
-    const int64_t num_slots = (int64_t)NB * block_size;
-    if ((rc = make_cache_map(&tm_k, k_cache, num_slots, KVH))) return rc;
-    if ((rc = make_cache_map(&tm_v, v_cache, num_slots, KVH))) return rc;
-
-    Params p;
-    p.q = (const __nv_bfloat16*)q;
-    p.block_tables = block_tables;
-    p.context_lens = context_lens;
-    p.out = (__nv_bfloat16*)out;
-    p.prefix = (int32_t*)workspace;
-    p.partials = (float*)((uint8_t*)workspace + round256((size_t)(B + 1) * 4));
-    p.B = B;
-    p.H = H;
-    p.KVH = KVH;
-    p.G = H / KVH;
-    p.NB = NB;
-    p.block_size = block_size;
-    p.MB = MB;
-    p.num_groups = grid / KVH;
-    p.scale_log2 = scale * 1.4426950408889634f;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.num_groups * KVH));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cfg.stream = st;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_kernel, tm_k, tm_v, p));
-    cfg.gridDim = dim3((unsigned)(B * KVH * p.G));
-    cfg.blockDim = dim3(kD);
-    cfg.dynamicSmemBytes = 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel, p));
-    return NVLLM_B200_OK;
+extern "C" int nvllm_b200_decode_step(const void* q, const void* k, const void* v, void* k_cache, void* v_cache,
+                                      const int32_t* slot_mapping, const int32_t* block_tables,
+                                      const int32_t* context_lens, void* out, void* workspace, size_t workspace_bytes,
+                                      int B, int H, int KVH, int D, int NB, int block_size, int MB, float scale,
+                                      int src_dtype, void* stream) {
+    using namespace nvllm::decode;
+    const DecodeArgs a = {q, k_cache, v_cache, block_tables, context_lens, out, B, H, KVH, D, NB, block_size, MB, scale,
+                          stream};
+    const StepArgs s = {k, v, slot_mapping, src_dtype};
+    return decode_with_workspace("decode_step", a, &s, workspace, workspace_bytes);
 }
 
 namespace nvllm {
@@ -607,16 +758,17 @@ int read_decode_flags(int* out) {
 // split-K scratch of the decode kernels lives in this fixed array, which every device that loads the
 // library carries until the process exits.
 //
-// Sizes are capped so the array stays small: batch <= kStaticMaxBatch and a main grid of at most
+// Sizes are capped so the array stays small: B * KVH <= kStaticMaxTickets and a main grid of at most
 // kStaticMaxCtas CTAs (2 per SM, i.e. devices with up to 160 SMs).
 namespace nvllm {
 namespace decode {
 
 constexpr int kStaticMaxBatch = 4096;
+constexpr int kStaticMaxTickets = kStaticMaxBatch * 8;
 constexpr int kStaticMaxCtas = 320;
-constexpr size_t kStaticPrefixBytes = ((size_t)(kStaticMaxBatch + 1) * 4 + 255) & ~size_t(255);
+constexpr size_t kStaticTicketBytes = (size_t)kStaticMaxTickets * 4;
 constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxCtas * 2 * ((size_t)kMaxG * kD + 2 * kMaxG) * 4;
-constexpr size_t kStaticScratchBytes = kStaticPrefixBytes + kStaticPartialBytes;  // about 2.7 MB
+constexpr size_t kStaticScratchBytes = kStaticTicketBytes + kStaticPartialBytes;  // about 2.8 MB
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -651,77 +803,24 @@ extern "C" int nvllm_b200_paged_decode_static(const void* q, const void* k_cache
                                               float scale, void* stream) {
     using namespace nvllm;
     using namespace nvllm::decode;
-    if (B < 0 || H <= 0 || KVH <= 0 || NB <= 0 || block_size <= 0 || MB <= 0)
-        return fail(NVLLM_B200_EINVAL, "paged_decode_static: non-positive size (B=%d H=%d KVH=%d NB=%d block=%d MB=%d)",
-                    B, H, KVH, NB, block_size, MB);
-    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: head_dim %d (only 128)", D);
-    if (block_size % kTile != 0)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: block_size %d must be a multiple of %d", block_size,
-                    kTile);
-    if (H % KVH != 0 || H / KVH > kMaxG)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: H/KVH = %d/%d must be an integer <= %d", H, KVH,
-                    kMaxG);
-    if ((long long)MB * block_size > 0x3fffffffLL || (long long)NB * block_size > 0x7fffffffLL)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: cache or context too large for 32-bit token indices");
-    if (B > kStaticMaxBatch)
+    const char* who = "paged_decode_static";
+    const DecodeArgs a = {q, k_cache, v_cache, block_tables, context_lens, out, B, H, KVH, D, NB, block_size, MB, scale,
+                          stream};
+    int rc = check_decode_args(who, a);
+    if (rc) return rc;
+    if (B > kStaticMaxBatch || (long long)B * KVH > kStaticMaxTickets)
         return fail(NVLLM_B200_EWORKSPACE,
-                    "paged_decode_static: batch %d exceeds the built-in scratch (max %d sequences); use "
-                    "nvllm_b200_paged_decode with a caller workspace",
-                    B, kStaticMaxBatch);
-    const int grid = main_grid();
-    if (grid > kStaticMaxCtas)
+                    "paged_decode_static: batch %d x %d kv heads exceeds the built-in scratch (max %d sequences and "
+                    "%d sequence-heads); use nvllm_b200_paged_decode with a caller workspace",
+                    B, KVH, kStaticMaxBatch, kStaticMaxTickets);
+    if (main_grid() > kStaticMaxCtas)
         return fail(NVLLM_B200_EWORKSPACE,
                     "paged_decode_static: this device needs %d CTAs, the built-in scratch holds %d; use "
                     "nvllm_b200_paged_decode with a caller workspace",
-                    grid, kStaticMaxCtas);
+                    main_grid(), kStaticMaxCtas);
     if (B == 0) return NVLLM_B200_OK;
-    if (!q || !k_cache || !v_cache || !block_tables || !context_lens || !out)
-        return fail(NVLLM_B200_EINVAL, "paged_decode_static: null pointer");
-    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
-        return fail(NVLLM_B200_EINVAL, "paged_decode_static: q/k_cache/v_cache/out must be 16-byte aligned");
-    if (KVH > grid)
-        return fail(NVLLM_B200_EUNSUPPORTED, "paged_decode_static: KVH %d exceeds the CTA count %d", KVH, grid);
-    int rc = ensure_smem_attr();
-    if (rc) return rc;
+    if ((rc = check_decode_pointers(who, a))) return rc;
     void* scratch = nullptr;
     if ((rc = static_scratch_address(&scratch))) return rc;
-
-    CUtensorMap tm_k, tm_v;
-    const int64_t num_slots = (int64_t)NB * block_size;
-    if ((rc = make_cache_map(&tm_k, k_cache, num_slots, KVH))) return rc;
-    if ((rc = make_cache_map(&tm_v, v_cache, num_slots, KVH))) return rc;
-
-    Params p;
-    p.q = (const __nv_bfloat16*)q;
-    p.block_tables = block_tables;
-    p.context_lens = context_lens;
-    p.out = (__nv_bfloat16*)out;
-    p.prefix = (int32_t*)scratch;
-    p.partials = (float*)((uint8_t*)scratch + kStaticPrefixBytes);
-    p.B = B;
-    p.H = H;
-    p.KVH = KVH;
-    p.G = H / KVH;
-    p.NB = NB;
-    p.block_size = block_size;
-    p.MB = MB;
-    p.num_groups = grid / KVH;
-    p.scale_log2 = scale * 1.4426950408889634f;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.num_groups * KVH));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cfg.stream = st;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_kernel, tm_k, tm_v, p));
-    cfg.gridDim = dim3((unsigned)(B * KVH * p.G));
-    cfg.blockDim = dim3(kD);
-    cfg.dynamicSmemBytes = 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel, p));
-    return NVLLM_B200_OK;
+    return launch_decode(who, a, nullptr, (unsigned int*)scratch, (float*)((uint8_t*)scratch + kStaticTicketBytes));
 }

@@ -102,6 +102,12 @@ class Attention:
 
     def __call__(self, q, k, v, context: AttentionContext):
         """q [T, H, D]; k, v [T, KVH, D]; returns [T, H, D].  Stores k/v first, then attends (reference :436-480)."""
+        if not context.is_prefill and self.k_cache is not None and self.v_cache is not None:
+            # decode: the scatter of the step's K/V rows and the attention over the pages go down as one C call
+            # (same result as the two calls of the reference, :465-467 then :476-478)
+            return ops.decode_step(q.to(self.k_cache.dtype).contiguous(), k.contiguous(), v.contiguous(),
+                                   self.k_cache, self.v_cache, context.slot_mapping, context.block_tables,
+                                   context.context_lens, self.scale, self.block_size)
         if self.k_cache is not None and self.v_cache is not None:
             num_blocks = self.k_cache.shape[0]
             flat = (num_blocks * self.block_size, self.num_kv_heads, self.head_dim)

@@ -111,6 +111,48 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return out
 
 
+def decode_step(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                slot_mapping: torch.Tensor, block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float,
+                block_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One decode step of one layer in one C call: scatter key/value [B, KVH, D] into the cache by slot, then
+    attend (same result as ``store_kvcache`` followed by ``paged_decode``).  Caches are [NB, block, KVH, D]."""
+    if key.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"key must be bf16 or fp32, got {key.dtype}")
+    _need(q, "q", torch.bfloat16, 3)
+    _need(key, "key", key.dtype, 3)
+    _need(value, "value", key.dtype, 3)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    _need(block_tables, "block_tables", torch.int32, 2)
+    _need(context_lens, "context_lens", torch.int32, 1)
+    b, h, d = q.shape
+    nb, blk, kvh, d2 = k_cache.shape
+    if v_cache.shape != k_cache.shape or d2 != d or blk != block_size:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} inconsistent with q {tuple(q.shape)} / block {block_size}")
+    if tuple(key.shape) != (b, kvh, d) or value.shape != key.shape:
+        raise ValueError(f"key/value must be [{b}, {kvh}, {d}], got {tuple(key.shape)} / {tuple(value.shape)}")
+    if block_tables.shape[0] != b or context_lens.shape[0] != b or slot_mapping.shape[0] != b:
+        raise ValueError("block_tables / context_lens / slot_mapping batch mismatch")
+    mb = block_tables.shape[1]
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _need(out, "out", torch.bfloat16, 3)
+        if out.shape != q.shape:
+            raise ValueError("out shape mismatch")
+    with torch.cuda.device(q.device):
+        lib = _lib.load()
+        need = int(lib.nvllm_b200_paged_decode_workspace_bytes(b, h, kvh, d, mb, block_size))
+        scratch = workspace(q.device, need)
+        _lib.check(lib.nvllm_b200_decode_step(
+            q.data_ptr(), key.data_ptr(), value.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            slot_mapping.data_ptr(), block_tables.data_ptr(), context_lens.data_ptr(), out.data_ptr(),
+            scratch.data_ptr(), scratch.numel(), b, h, kvh, d, nb, block_size, mb, float(scale),
+            _lib.DTYPE_BF16 if key.dtype == torch.bfloat16 else _lib.DTYPE_F32, _stream_ptr(q.device)))
+    return out
+
+
 def varlen_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
                    scale: float, out: torch.Tensor | None = None, cu_seqlens_host=None,
                    cu_seqlens_k: torch.Tensor | None = None) -> torch.Tensor:

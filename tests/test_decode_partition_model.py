@@ -1,7 +1,8 @@
-"""CPU model of the integer logic of the paged-decode kernels (csrc/paged_decode.cu): the stream-K cut of the tile
-stream into per-CTA ranges, which ranges emit a partial result into which workspace slot, and which slots the merge
-kernel reads back.  Property-tested against brute force: every tile is served exactly once, every output row is
-written exactly once, and the merge kernel reads exactly the slots that were written for its sequence."""
+"""CPU model of the integer logic of the paged-decode kernel (csrc/paged_decode.cu): the stream-K cut of the tile
+stream into per-CTA ranges, which ranges emit a partial result into which workspace slot, how many tickets a split
+sequence expects before it is combined, and which slots the combining CTA reads back.  Property-tested against brute
+force: every tile is served exactly once, every output row is written exactly once, the ticket count equals the
+number of partials written, and the combine step reads exactly the slots that were written for its sequence."""
 import numpy as np
 from hypothesis import given, settings, strategies as st
 
@@ -43,8 +44,15 @@ def main_kernel_model(ctx, num_groups):
     return direct, partial, served[:total], prefix, total
 
 
+def expected_tickets(first, tb, total, num_groups):
+    """The kernel's `parts`: tickets a split sequence collects before the last arrival combines its partials."""
+    if total >= num_groups:
+        return ((first + tb) * num_groups - 1) // total - ((first + 1) * num_groups - 1) // total + 1
+    return tb
+
+
 def merge_kernel_model(b, prefix, total, num_groups):
-    """Slots the merge kernel reads for sequence b ('zero' if it writes a zero row, None if it does nothing)."""
+    """Slots merge_sequence reads for sequence b ('zero' if the row is zero-filled, None if nothing is combined)."""
     first, tb = int(prefix[b]), int(prefix[b + 1] - prefix[b])
     if tb == 0:
         return "zero"
@@ -79,6 +87,7 @@ def test_every_tile_once_and_merge_reads_what_was_written(ctx, num_groups):
             pieces = sorted(by_seq[b])
             assert want is not None and want != "zero"
             assert sorted(want) == [(g, s) for g, s, _, _ in pieces], (ctx, num_groups, b, want, pieces)
+            assert expected_tickets(int(prefix[b]), tiles_of(c), total, num_groups) == len(pieces)
             # the pieces tile the sequence without gap or overlap
             spans = sorted((t0, t1) for _, _, t0, t1 in pieces)
             assert spans[0][0] == 0 and spans[-1][1] == tiles_of(c)

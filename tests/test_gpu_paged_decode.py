@@ -207,7 +207,8 @@ def _sampled_check(w, n_sample, seed, what):
     assert torch.isfinite(out.float()).all()
     rng = np.random.Generator(np.random.PCG64(seed))
     order = np.argsort(w.context_lens)
-    pick = set(order[:2].tolist() + order[-2:].tolist() + rng.choice(w.batch, n_sample, replace=False).tolist())
+    pick = set(order[:4].tolist() + order[-4:].tolist()
+               + rng.choice(w.batch, min(n_sample, w.batch), replace=False).tolist())
     worst = 0.0
     for b in sorted(pick):
         ids = [i for i in w.block_lists[b]]
@@ -223,16 +224,59 @@ def _sampled_check(w, n_sample, seed, what):
     return worst
 
 
-def test_config2_full_size_sampled():
-    """Qwen3-8B, batch 64, ctx U[512, 8192], 4096-block pool (4.3 GB of cache): sampled sequences vs oracle."""
+def test_config2_full_size_every_sequence():
+    """Qwen3-8B, batch 64, ctx U[512, 8192], 4096-block pool (4.3 GB of cache): all 64 sequences vs the oracle."""
     from nanovllm_jax_b200 import workloads
-    _sampled_check(workloads.config2(), 6, 2000, "cfg2")
+    w = workloads.config2()
+    _sampled_check(w, w.batch, 2000, "cfg2")
 
 
 def test_config3_skewed_long_context_sampled():
-    """Qwen3-32B shapes, batch 256, log-uniform ctx in [16, 32768], G = 8: shortest, longest and random sequences."""
+    """Qwen3-32B shapes, batch 256, log-uniform ctx in [16, 32768], G = 8: the 4 shortest, the 4 longest and 28
+    random sequences."""
     from nanovllm_jax_b200 import workloads
-    _sampled_check(workloads.config3(), 6, 3000, "cfg3")
+    _sampled_check(workloads.config3(), 28, 3000, "cfg3")
+
+
+@pytest.mark.parametrize("src", ["bf16", "f32"])
+def test_decode_step_equals_store_then_decode(src):
+    """nvllm_b200_decode_step (one C call) against nvllm_b200_store_kvcache + nvllm_b200_paged_decode: caches and
+    outputs bit for bit, and the output against the oracle run on the oracle's own updated cache."""
+    import torch
+    from nanovllm_jax_b200 import ops, workloads
+    from oracle import reference_attention as ref
+    w = workloads.make_decode_workload("step", seed=91, batch=33, num_heads=32, num_kv_heads=8, num_blocks=200,
+                                       ctx_lo=1, ctx_hi=1500, max_blocks=6)
+    t = workloads.decode_tensors_numpy(w)
+    w.slot_mapping[5] = -1  # a padded row of a fixed-shape batch: nothing is stored for it
+    rng = np.random.Generator(np.random.PCG64(5))
+    k_new = rng.standard_normal((w.batch, 8, 128), dtype=np.float32)
+    v_new = rng.standard_normal((w.batch, 8, 128), dtype=np.float32)
+    if src == "bf16":
+        k_new, v_new = ref.round_to_bf16(k_new), ref.round_to_bf16(v_new)
+    flat = (w.num_blocks * w.block_size, 8, 128)
+    kcb, vcb = ref.store_kv_to_cache(k_new, v_new, t["k_cache_bits"].reshape(flat), t["v_cache_bits"].reshape(flat),
+                                     w.slot_mapping, skip_negative=True)
+    shape4 = t["k_cache_bits"].shape
+    want = ref.paged_decode_attention_streamed(t["q"], kcb.reshape(shape4), vcb.reshape(shape4), w.block_tables,
+                                               w.context_lens, w.scale, w.block_size, kv_dtype_bits=True)
+    dt = torch.bfloat16 if src == "bf16" else torch.float32
+    k_dev, v_dev = torch.from_numpy(k_new).cuda().to(dt), torch.from_numpy(v_new).cuda().to(dt)
+    q = bits_to_torch(t["q_bits"])
+    sl = torch.from_numpy(w.slot_mapping).cuda()
+    bt = torch.from_numpy(w.block_tables).cuda()
+    cl = torch.from_numpy(w.context_lens).cuda()
+    kc1, vc1 = bits_to_torch(t["k_cache_bits"]), bits_to_torch(t["v_cache_bits"])
+    kc2, vc2 = kc1.clone(), vc1.clone()
+    ops.store_kvcache(k_dev, v_dev, kc1.view(flat), vc1.view(flat), sl)
+    two = ops.paged_decode(q, kc1, vc1, bt, cl, w.scale, w.block_size)
+    one = ops.decode_step(q, k_dev, v_dev, kc2, vc2, sl, bt, cl, w.scale, w.block_size)
+    torch.cuda.synchronize()
+    assert np.array_equal(torch_to_bits(kc2).reshape(flat), kcb) and np.array_equal(torch_to_bits(vc2).reshape(flat), vcb)
+    assert np.array_equal(torch_to_bits(kc1), torch_to_bits(kc2))
+    assert np.array_equal(torch_to_bits(one), torch_to_bits(two))
+    assert_attention_close(torch_to_f32(one), want, "decode_step")
+    _status_clean()
 
 
 @pytest.mark.parametrize("tp", [2, 4, 8])
