@@ -160,7 +160,9 @@ int nvllm_b200_paged_decode_static(const void* q, const void* k_cache, const voi
  * Reads (and leaves set) the device-side error flags of the current device into
  * *flags_host.  0 = no kernel of this library ever gave up a bounded wait.
  * Bit 0 / 1: paged_decode producer / consumer timed out on a pipeline barrier.
- * Bit 2 / 3: varlen_prefill pipeline wait timed out / TMEM allocation failed.
+ * Bit 2 (4): a prefill pipeline wait timed out.  Bit 4 (16): a sequence too long
+ * for the prefill plan.  Bit 5 (32): prefill called with inconsistent
+ * cu_seqlens_q / cu_seqlens_k (see nvllm_b200_varlen_prefill / _paged_prefill).
  * This call synchronises with the device (it copies one int back).
  */
 int nvllm_b200_device_status(int* flags_host);
@@ -178,7 +180,10 @@ size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KV
  *   q             [T, H, D] bf16;  k, v [T, KVH, D] bf16;  out [T, H, D] bf16
  *   cu_seqlens_q, cu_seqlens_k  [B+1] int32 DEVICE arrays; they must be equal
  *                 element-wise (prompt without cached prefix -- the only case in
- *                 which the reference function is correct); cu_seqlens_host, if
+ *                 which the reference function is correct).  The device checks
+ *                 it: if they differ nothing is computed and bit 5 (32) of the
+ *                 device status is raised -- a prompt with a cached prefix goes
+ *                 to nvllm_b200_paged_prefill.  cu_seqlens_host, if
  *                 not NULL, is a host copy of cu_seqlens_q that lets the library
  *                 size its grid without reading device memory
  *   max_seqlen    upper bound of any sequence length (used for grid sizing when
@@ -194,6 +199,48 @@ int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v,
                               void* workspace, size_t workspace_bytes,
                               int64_t T, int B, int max_seqlen, int H, int KVH, int D,
                               float scale, void* stream);
+
+/*
+ * paged_prefill: causal attention of the new tokens of B sequences over ALL their
+ * tokens, cached prefix included, with keys/values read from the paged cache:
+ * query i of sequence b sits at position prefix_b + i, prefix_b = len_k - len_q,
+ * and attends positions 0 .. prefix_b + i of the pages block_tables[b, :].
+ *
+ * This is the prefill the reference's metadata asks for on a prefix-cache hit and
+ * its attention code does not deliver: engine/model_runner.py:286-292 emits
+ * cu_seqlens_k > cu_seqlens_q and :311-314 attaches block_tables, but
+ * Attention._prefill_attention (layers/attention.py:351-364) drops the tables and
+ * attends the new tokens only.  It replaces that branch, and it is what makes the
+ * block manager's prefix cache (engine/block_manager.py:137-182) usable.  With
+ * cu_seqlens_k == cu_seqlens_q it computes what nvllm_b200_varlen_prefill does.
+ *
+ *   q, out        [T, H, D] bf16, new tokens packed by cu_seqlens_q
+ *   k_cache, v_cache [NB, block_size, KVH, D] bf16; the step's new K/V rows must
+ *                 already be stored (Attention.__call__ stores before it attends,
+ *                 layers/attention.py:465-467); block_size a multiple of 128
+ *   cu_seqlens_q, cu_seqlens_k [B+1] int32 device arrays (only the differences of
+ *                 cu_seqlens_k are used: the key count of each sequence);
+ *                 len_k >= len_q for every sequence, else nothing is computed and
+ *                 bit 5 (32) of the device status is raised
+ *   block_tables  [B, MB] int32, -1 padded
+ *   cu_seqlens_q_host  optional host copy of cu_seqlens_q (exact grid sizing)
+ *   workspace     >= nvllm_b200_varlen_prefill_workspace_bytes(T, B, H, KVH, D)
+ *
+ * Cache rows at positions >= len_k are never used, whatever they hold.
+ */
+int nvllm_b200_paged_prefill(const void* q, const void* k_cache, const void* v_cache,
+                             const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                             const int32_t* block_tables, const int32_t* cu_seqlens_q_host, void* out,
+                             void* workspace, size_t workspace_bytes,
+                             int64_t T, int B, int max_seqlen_q, int H, int KVH, int D,
+                             int NB, int block_size, int MB, float scale, void* stream);
+
+/*
+ * Clears the device-side error flags of the current device (see
+ * nvllm_b200_device_status).  A host that has read and handled a non-zero status
+ * calls this before it goes on.  Synchronises with the device.
+ */
+int nvllm_b200_device_status_reset(void);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,8 @@ SIGNATURES = {
     "nvllm_b200_device_status": (_i32, [_c.POINTER(_i32)]),
     "nvllm_b200_varlen_prefill_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),
     "nvllm_b200_varlen_prefill": (_i32, [_vp] * 8 + [_sz, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "nvllm_b200_paged_prefill": (_i32, [_vp] * 9 + [_sz, _i64] + [_i32] * 8 + [_f32, _vp]),
+    "nvllm_b200_device_status_reset": (_i32, []),
 }
 
 _lock = threading.Lock()
@@ -70,3 +72,7 @@ def device_status() -> int:
     flags = _i32(0)
     check(load().nvllm_b200_device_status(ctypes.byref(flags)))
     return int(flags.value)
+
+
+def device_status_reset() -> None:
+    check(load().nvllm_b200_device_status_reset())

@@ -50,7 +50,7 @@ bool pdl_enabled() {
 
 }  // namespace nvllm
 
-extern "C" int nvllm_b200_version(void) { return 100; }
+extern "C" int nvllm_b200_version(void) { return 200; }
 
 extern "C" const char* nvllm_b200_last_error_string(void) { return nvllm::last_error_buffer(); }
 
@@ -62,4 +62,11 @@ extern "C" int nvllm_b200_device_status(int* flags_host) {
     if ((rc = read_prefill_flags(&b))) return rc;
     *flags_host = a | b;
     return NVLLM_B200_OK;
+}
+
+extern "C" int nvllm_b200_device_status_reset(void) {
+    using namespace nvllm;
+    int rc;
+    if ((rc = clear_decode_flags())) return rc;
+    return clear_prefill_flags();
 }

@@ -746,6 +746,11 @@ int read_decode_flags(int* out) {
     NVLLM_CUDA_OK(cudaMemcpyFromSymbol(out, decode::g_error_flag, sizeof(int)));
     return NVLLM_B200_OK;
 }
+int clear_decode_flags() {
+    const int zero = 0;
+    NVLLM_CUDA_OK(cudaMemcpyToSymbol(decode::g_error_flag, &zero, sizeof(int)));
+    return NVLLM_B200_OK;
+}
 }  // namespace nvllm
 
 // ---------------------------------------------------------------------------

@@ -2,7 +2,12 @@
 // sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // Replaces variable_length_attention_prefill (reference layers/attention.py:135-279)
-// and paged_prefill_attention (layers/pallas_attention.py:557-608).
+// and paged_prefill_attention (layers/pallas_attention.py:557-608).  Keys and values
+// are either packed like the queries ([T, KVH, 128], cu_seqlens_k == cu_seqlens_q) or
+// read from the paged cache through block tables (prefix-cached prefill,
+// cu_seqlens_k >= cu_seqlens_q: query i of a sequence sits at position prefix + i,
+// prefix = len_k - len_q; the model runner attaches the tables on a prefix hit,
+// engine/model_runner.py:311-314).
 //
 // Work item = 256 consecutive query rows of one sequence for one query head, handled
 // as two 128-row Q tiles (A and B) that share every K/V tile they read.  A tiny plan
@@ -45,7 +50,9 @@
 namespace nvllm {
 namespace prefill {
 
-__device__ int g_error_flag = 0;  // bit 2: pipeline wait timed out; bit 4: sequence too long for the plan kernel
+// bit 2 (4): pipeline wait timed out; bit 4 (16): sequence too long for the plan kernel; bit 5 (32): a sequence has
+// fewer keys than queries, or (packed keys) a different number -- nothing is computed for that call
+__device__ int g_error_flag = 0;
 
 constexpr int kD = 128;
 constexpr int kTileQ = 128;            // rows per Q tile
@@ -62,8 +69,12 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Params {
-    const int4* items;  // record 0: {number of (sequence, row block) pairs, 0, 0, 0}; record 1+i: {first token of the
-                        // sequence, its length, first row of the block, 0}, longest causal span first
+    const int4* items;  // record 0: {number of (sequence, row block) pairs, 0, 0, 0}; record 1+i: {first query token of
+                        // the sequence, its query length, first row of the block, sequence index}, longest causal span
+                        // first
+    const int32_t* cu_k;          // [B+1] key offsets: packed keys = token offsets into k/v; paged = lengths only
+    const int32_t* block_tables;  // [B, MB] page ids, or nullptr for packed keys/values
+    int MB, block_size;
     __nv_bfloat16* out;
     int H, G;
     float scale_log2;
@@ -210,27 +221,43 @@ constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);  // B operand MN-major
 // ------------------------------------------------------------------------------------------
 // plan kernel: (sequence, 256-row block) pairs sorted by block index, largest first
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens, int B,
+__global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens,
+                                                            const int32_t* __restrict__ cu_k, int paged, int B,
                                                             int4* __restrict__ items, int capacity) {
+    // A row block's weight is its causal span in 256-key units: level = prefix / 256 + block index.
     __shared__ int hist[kMaxLevels];
     __shared__ int base[kMaxLevels];
-    __shared__ int max_level;
+    __shared__ int max_level, bad;
     griddep_wait();
     griddep_launch_dependents();
     for (int i = threadIdx.x; i < kMaxLevels; i += blockDim.x) hist[i] = 0;
-    if (threadIdx.x == 0) max_level = 0;
+    if (threadIdx.x == 0) max_level = 0, bad = 0;
     __syncthreads();
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         const int len = cu_seqlens[b + 1] - cu_seqlens[b];
-        int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
-        if (n > kMaxLevels) {
-            n = kMaxLevels;
-            atomicOr(&g_error_flag, 16);
+        const int len_k = cu_k[b + 1] - cu_k[b];
+        // keys can never be fewer than queries; packed keys sit beside the queries, so the counts must be equal
+        if (len > 0 && (len_k < len || (!paged && (len_k != len || cu_k[b] != cu_seqlens[b])))) bad = 1;
+        const int lvl0 = len_k > len ? (len_k - len) / kBlockQ : 0;
+        const int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
+        for (int l = 0; l < n; ++l) {
+            int lvl = lvl0 + l;
+            if (lvl >= kMaxLevels) {
+                lvl = kMaxLevels - 1;
+                atomicOr(&g_error_flag, 16);
+            }
+            atomicAdd(&hist[lvl], 1);
+            atomicMax(&max_level, lvl + 1);
         }
-        for (int l = 0; l < n; ++l) atomicAdd(&hist[l], 1);
-        atomicMax(&max_level, n);
     }
     __syncthreads();
+    if (bad) {  // uniform: publish an empty list so that the main kernel computes nothing
+        if (threadIdx.x == 0) {
+            items[0] = make_int4(0, 0, 0, 0);
+            atomicOr(&g_error_flag, 32);
+        }
+        return;
+    }
     if (threadIdx.x == 0) {
         int run = 0;
         for (int l = max_level - 1; l >= 0; --l) {
@@ -243,11 +270,13 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
     for (int b = threadIdx.x; b < B; b += blockDim.x) {
         const int start = cu_seqlens[b];
         const int len = cu_seqlens[b + 1] - start;
-        int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
-        if (n > kMaxLevels) n = kMaxLevels;
+        const int len_k = cu_k[b + 1] - cu_k[b];
+        const int lvl0 = len_k > len ? (len_k - len) / kBlockQ : 0;
+        const int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
         for (int l = 0; l < n; ++l) {
-            const int slot = atomicAdd(&base[l], 1);
-            if (slot < capacity) items[1 + slot] = make_int4(start, len, l * kBlockQ, 0);
+            const int lvl = min(lvl0 + l, kMaxLevels - 1);
+            const int slot = atomicAdd(&base[lvl], 1);
+            if (slot < capacity) items[1 + slot] = make_int4(start, len, l * kBlockQ, b);
         }
     }
 }
@@ -260,6 +289,7 @@ struct Shared {
     uint64_t kv_full[kSlots], kv_empty[kSlots];
     uint64_t s_full[2], p_full[2][2], o_full[2], o_empty[2];
     uint64_t turn[2];  // softmax ping-pong: turn[0] = "tile A finished a softmax", turn[1] = "tile B finished one"
+    uint64_t fix_full, fix_empty;  // last V tile of a sequence: rows past the sequence's end have been zeroed / used
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -273,8 +303,10 @@ __device__ __forceinline__ bool wait_or_abort(Shared* sh, uint64_t* bar, uint32_
 }
 
 struct Item {
-    int seq_start, len, q0, head;
-    int n_a, n_b, n_kv;  // KV tiles seen by Q tile A, by Q tile B (one more: its diagonal), and the larger
+    int seq_start, len, q0, head, b;  // first query token of the sequence, query length, first row of the block
+    int k_start, len_k, prefix;       // first key token (packed keys), key length, len_k - len
+    int n_a, n_b, n_kv;  // KV tiles seen by Q tile A, by Q tile B (0: no such rows; else n_a or n_a + 1), and the larger
+    bool ragged;         // the last KV tile reaches past the sequence's last key
 };
 
 __device__ __forceinline__ Item load_item(const Params& p, int idx) {
@@ -285,19 +317,36 @@ __device__ __forceinline__ Item load_item(const Params& p, int idx) {
     it.seq_start = r.x;
     it.len = r.y;
     it.q0 = r.z;
+    it.b = r.w;
+    it.k_start = __ldg(p.cu_k + it.b);
+    it.len_k = __ldg(p.cu_k + it.b + 1) - it.k_start;
+    it.prefix = it.len_k - it.len;  // >= 0: the plan kernel publishes no items otherwise
     const int rows = min(kBlockQ, it.len - it.q0);
-    it.n_a = it.q0 / kTileKV + 1;
-    it.n_b = rows > kTileQ ? it.q0 / kTileKV + 2 : 0;
+    const int nk_total = (it.len_k + kTileKV - 1) / kTileKV;
+    // the last row of Q tile x sees keys 0 .. prefix + q0 + 128 x + 127
+    it.n_a = min(nk_total, (it.prefix + it.q0 + kTileQ - 1) / kTileKV + 1);
+    it.n_b = rows > kTileQ ? min(nk_total, (it.prefix + it.q0 + 2 * kTileQ - 1) / kTileKV + 1) : 0;
     it.n_kv = max(it.n_a, it.n_b);
+    it.ragged = it.n_kv * kTileKV > it.len_k;
     return it;
 }
 
-// One 128-column S row -> running max, optional O rescale, bf16 P in two halves.  DIAG: key c visible iff c <= row.
+// First token (row of the k / v tensor map) of KV tile j of the item's sequence.
+__device__ __forceinline__ int kv_tile_token(const Params& p, const Item& it, int j) {
+    const int off = j * kTileKV;
+    if (p.block_tables == nullptr) return it.k_start + off;
+    int page = __ldg(p.block_tables + (size_t)it.b * p.MB + off / p.block_size);
+    if (page < 0) page = 0;  // a padding entry: never reached for keys below len_k
+    return page * p.block_size + off % p.block_size;  // block_size is a multiple of the tile: a tile never straddles pages
+}
+
+// One 128-column S row -> running max, optional O rescale, bf16 P in two halves.  DIAG: key column c of this tile is
+// visible iff c <= lim (lim may be negative -- nothing visible in this tile -- or >= 127).
 // The whole row is held in registers (the softmax warpgroups raise their register budget with setmaxnreg), so
 // tensor memory is read once and its latency is paid once per tile.
 template <bool DIAG>
 __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint32_t t_s, const uint32_t t_o,
-                                             const int row, const bool first, const uint32_t o_parity_prev,
+                                             const int lim, const bool first, const uint32_t o_parity_prev,
                                              const float scale_log2, float& m_run, float& m_used, float& l) {
     uint32_t v[4][32];
     tmem_ld32(t_s, v[0]);
@@ -313,7 +362,7 @@ __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint
             if (DIAG) {  // mask in place so that the second pass needs no select
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                    if (c * 32 + i + u > row) v[c][i + u] = 0xFF800000u;
+                    if (c * 32 + i + u > lim) v[c][i + u] = 0xFF800000u;
             }
             mx0 = max3(mx0, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
             mx1 = max3(mx1, __uint_as_float(v[c][i + 2]), __uint_as_float(v[c][i + 3]));
@@ -323,7 +372,7 @@ __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint
     }
     m_run = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
     if (first) {
-        m_used = m_run;
+        m_used = m_run;  // finite: key 0 of the sequence is visible to every row and sits in the first tile
     } else {
         const bool grow = (m_run - m_used) * scale_log2 > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
@@ -406,6 +455,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(&sh->o_empty[x], kTileQ / 32);
             mbar_init(&sh->turn[x], kTileQ / 32);
         }
+        mbar_init(&sh->fix_full, 1);
+        mbar_init(&sh->fix_empty, 2);  // both MMA issuers
         sh->abort_flag = 0;
         sh->tmem_base = 0xFFFFFFFFu;
         fence_mbar_init();
@@ -451,7 +502,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q + kTileQ);
                 }
                 for (int j = 0; j < it.n_kv; ++j, ++kt) {
-                    const int tok = it.seq_start + j * kTileKV;
+                    const int tok = kv_tile_token(p, it, j);
 #pragma unroll
                     for (int kv = 0; kv < 2; ++kv) {  // K(j) then V(j): with five slots both are requested ~2 tiles ahead
                         const uint32_t pos = 2 * kt + kv;
@@ -465,6 +516,39 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     if (!ok) break;
                 }
             }
+        }
+    } else if (warp == 3) {
+        // ================================ V-tile fixer ================================
+        // The last KV tile of a sequence reaches past its last key: those rows of the tile hold whatever follows
+        // in memory (the next sequence, padding, recycled cache rows).  Their probabilities are exactly zero, but
+        // 0 * NaN or 0 * Inf in the P.V product would still poison the row, so this warp zeroes them in the V tile
+        // once it has landed, before either MMA issuer may use it.  (Garbage in the K rows is harmless: those scores
+        // are overwritten with -inf by the mask.)
+        uint32_t kt = 0, fixes = 0;
+        bool ok = true;
+        for (int idx = first_idx; ok && idx < total; idx += stride) {
+            const Item it = load_item(p, idx);
+            if (it.ragged) {
+                const uint32_t vpos = 2 * (kt + it.n_kv - 1) + 1;
+                if (lane == 0) {
+                    ok = wait_or_abort(sh, &sh->kv_full[vpos % kSlots], (vpos / kSlots) & 1u);
+                    if (ok && fixes > 0) ok = wait_or_abort(sh, &sh->fix_empty, (fixes - 1) & 1u);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                uint8_t* tile = sKV + (vpos % kSlots) * kTileBytes;
+                const int r0 = it.len_k - (it.n_kv - 1) * kTileKV;  // first row past the sequence, 1..127
+                // a row is 128 contiguous bytes in each of the two 64-dim panels (the swizzle permutes inside a row)
+                for (int i = lane; i < (kTileKV - r0) * 16; i += 32) {
+                    const int r = r0 + (i >> 4), c = i & 15;
+                    *reinterpret_cast<uint4*>(tile + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async_smem();  // generic-proxy writes above must be visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->fix_full);
+                ++fixes;
+            }
+            kt += it.n_kv;
         }
     } else if (warp == 1 || warp == 2) {
         // ============================== MMA issuers ===============================
@@ -485,6 +569,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             uint32_t kt = 0;     // K/V tiles consumed before this item
             uint32_t tiles = 0;  // tiles finished by this Q tile, over all items (barrier phases)
             uint32_t used = 0;   // items in which this Q tile was active (o_empty phases)
+            uint32_t fixes = 0;  // sequence-final items seen (fix_full / fix_empty phases)
             int i = 0;
             bool ok = true;
 
@@ -533,6 +618,11 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int j = 0; ok && j < it.n_kv; ++j) {
                     const uint32_t vpos = 2 * (kt + j) + 1, kpos = vpos + 1;  // ring positions of V(j) and K(j+1)
                     if (!(ok = slot_full(vpos))) break;
+                    if (it.ragged && j == it.n_kv - 1) {
+                        // the fixer has zeroed the rows past the sequence's end; the slot is released only after this
+                        if (!(ok = wait_or_abort(sh, &sh->fix_full, fixes & 1u))) break;
+                        tc_fence_after();
+                    }
                     if (j < n_x) {
                         if (!(ok = issue_pv(j, v_desc0 + (vpos % kSlots) * kSlotStep))) break;
                         tc_commit(&sh->kv_empty[vpos % kSlots]);
@@ -550,6 +640,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                             mbar_arrive(&sh->kv_empty[kpos % kSlots]);
                         }
                     }
+                }
+                if (it.ragged) {
+                    mbar_arrive(&sh->fix_empty);
+                    ++fixes;
                 }
                 used += n_x > 0 ? 1 : 0;
                 kt += it.n_kv;
@@ -577,7 +671,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int n_x = x == 0 ? it.n_a : it.n_b;
             if (n_x == 0) continue;
             const bool both = it.n_b > 0;
-            const int q_pos = it.q0 + x * kTileQ + row;  // position within the sequence
+            const int q_pos = it.q0 + x * kTileQ + row;             // row of the sequence's query block
+            const int first_lim = it.prefix + it.q0 + x * kTileQ;  // last key visible to the first row of this Q tile
             float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
             for (int j = 0; ok && j < n_x; ++j, ++tiles) {
                 if (!(ok = wait_or_abort(sh, &sh->s_full[x], tiles & 1u))) break;
@@ -587,10 +682,13 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     ++turns_seen;
                 }
                 tc_fence_after();
-                if (j == n_x - 1)
-                    ok = softmax_tile<true>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+                // the tile needs masking iff its last key lies beyond what the first row may see (one tile when the
+                // prefix is a multiple of the tile, two otherwise)
+                if (j * kTileKV + kTileKV - 1 > first_lim)
+                    ok = softmax_tile<true>(sh, x, t_s, t_o, first_lim - j * kTileKV + row, j == 0, (tiles - 1) & 1u,
+                                            p.scale_log2, m_run, m_used, l);
                 else
-                    ok = softmax_tile<false>(sh, x, t_s, t_o, row, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+                    ok = softmax_tile<false>(sh, x, t_s, t_o, 0, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
                 // hand the turn over: A after each of its tiles, B while A still has a tile that will wait for it
                 if (both && (x == 0 || j + 1 < it.n_a)) {
                     __syncwarp();
@@ -668,47 +766,26 @@ static int ensure_attr() {
 
 static int64_t item_capacity(int64_t T, int B) { return T / kBlockQ + B + 1; }
 
-}  // namespace prefill
-
-int read_prefill_flags(int* out) {
-    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(out, prefill::g_error_flag, sizeof(int)));
-    return NVLLM_B200_OK;
-}
-namespace prefill {
-
-}  // namespace prefill
-}  // namespace nvllm
-
-extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KVH, int D) {
-    (void)H;
-    (void)KVH;
-    (void)D;
-    if (T < 0 || B < 0) return 256;
-    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 16;
-    return (n + 255) & ~size_t(255);
-}
-
-extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
-                                         const int32_t* cu_seqlens_k, const int32_t* cu_seqlens_host, void* out,
-                                         void* workspace, size_t workspace_bytes, int64_t T, int B, int max_seqlen,
-                                         int H, int KVH, int D, float scale, void* stream) {
-    using namespace nvllm;
-    using namespace nvllm::prefill;
+// Common launcher.  kv_tokens: extent of the token axis of k / v (T for packed tensors, the slot count of the cache).
+static int launch(const char* who, const void* q, const void* k, const void* v, int64_t kv_tokens,
+                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, const int32_t* block_tables, int MB,
+                  int block_size, const int32_t* cu_seqlens_host, void* out, void* workspace, size_t workspace_bytes,
+                  int64_t T, int B, int max_seqlen, int H, int KVH, int D, float scale, void* stream) {
     if (T < 0 || B < 0 || H <= 0 || KVH <= 0)
-        return fail(NVLLM_B200_EINVAL, "varlen_prefill: bad size (T=%lld B=%d H=%d KVH=%d)", (long long)T, B, H, KVH);
-    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: head_dim %d (only 128)", D);
-    if (H % KVH != 0) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: H %d not a multiple of KVH %d", H, KVH);
-    if (B > 65535) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: more than 65535 sequences");
-    if (T > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: more than 2^31-1 tokens");
-    if (!(scale > 0.f)) return fail(NVLLM_B200_EINVAL, "varlen_prefill: scale must be positive");
+        return fail(NVLLM_B200_EINVAL, "%s: bad size (T=%lld B=%d H=%d KVH=%d)", who, (long long)T, B, H, KVH);
+    if (D != kD) return fail(NVLLM_B200_EUNSUPPORTED, "%s: head_dim %d (only 128)", who, D);
+    if (H % KVH != 0) return fail(NVLLM_B200_EUNSUPPORTED, "%s: H %d not a multiple of KVH %d", who, H, KVH);
+    if (B > 65535) return fail(NVLLM_B200_EUNSUPPORTED, "%s: more than 65535 sequences", who);
+    if (T > 0x7fffffffLL || kv_tokens > 0x7fffffffLL)
+        return fail(NVLLM_B200_EUNSUPPORTED, "%s: more than 2^31-1 tokens", who);
+    if (!(scale > 0.f)) return fail(NVLLM_B200_EINVAL, "%s: scale must be positive", who);
     if (T == 0 || B == 0) return NVLLM_B200_OK;
-    if (!q || !k || !v || !cu_seqlens_q || !cu_seqlens_k || !out)
-        return fail(NVLLM_B200_EINVAL, "varlen_prefill: null pointer");
+    if (!q || !k || !v || !cu_seqlens_q || !cu_seqlens_k || !out) return fail(NVLLM_B200_EINVAL, "%s: null pointer", who);
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15)
-        return fail(NVLLM_B200_EINVAL, "varlen_prefill: q/k/v/out must be 16-byte aligned");
+        return fail(NVLLM_B200_EINVAL, "%s: q/k/v/out must be 16-byte aligned", who);
     const size_t need = nvllm_b200_varlen_prefill_workspace_bytes(T, B, H, KVH, D);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))
-        return fail(NVLLM_B200_EWORKSPACE, "varlen_prefill: workspace of %zu bytes required, got %zu", need,
+        return fail(NVLLM_B200_EWORKSPACE, "%s: workspace of %zu bytes required, got %zu", who, need,
                     workspace ? workspace_bytes : (size_t)0);
 
     // Upper bound of (sequence, 256-row block) pairs: exact from the host copy of cu_seqlens, else from max_seqlen.
@@ -718,32 +795,35 @@ extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const voi
         for (int b = 0; b < B; ++b) {
             const int64_t len = (int64_t)cu_seqlens_host[b + 1] - cu_seqlens_host[b];
             if (len < 0 || cu_seqlens_host[b + 1] > T)
-                return fail(NVLLM_B200_EINVAL, "varlen_prefill: cu_seqlens_host is not a non-decreasing prefix of T");
+                return fail(NVLLM_B200_EINVAL, "%s: cu_seqlens_host is not a non-decreasing prefix of T", who);
             if (len > (int64_t)kMaxLevels * kBlockQ)
-                return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: sequence of %lld tokens (max %d)", (long long)len,
+                return fail(NVLLM_B200_EUNSUPPORTED, "%s: sequence of %lld tokens (max %d)", who, (long long)len,
                             kMaxLevels * kBlockQ);
             pairs += (len + kBlockQ - 1) / kBlockQ;
         }
     } else {
-        if (max_seqlen <= 0) return fail(NVLLM_B200_EINVAL, "varlen_prefill: max_seqlen must be positive");
+        if (max_seqlen <= 0) return fail(NVLLM_B200_EINVAL, "%s: max_seqlen must be positive", who);
         if (max_seqlen > kMaxLevels * kBlockQ)
-            return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: max_seqlen %d (max %d)", max_seqlen,
-                        kMaxLevels * kBlockQ);
+            return fail(NVLLM_B200_EUNSUPPORTED, "%s: max_seqlen %d (max %d)", who, max_seqlen, kMaxLevels * kBlockQ);
         pairs = (int64_t)B * ((max_seqlen + kBlockQ - 1) / kBlockQ);
     }
     if (pairs > cap) pairs = cap;
     if (pairs == 0) return NVLLM_B200_OK;
-    if (pairs * H > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "varlen_prefill: grid too large");
+    if (pairs * H > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "%s: grid too large", who);
 
     int rc = ensure_attr();
     if (rc) return rc;
     CUtensorMap tm_q, tm_k, tm_v;
     if ((rc = make_map(&tm_q, q, H, T))) return rc;
-    if ((rc = make_map(&tm_k, k, KVH, T))) return rc;
-    if ((rc = make_map(&tm_v, v, KVH, T))) return rc;
+    if ((rc = make_map(&tm_k, k, KVH, kv_tokens))) return rc;
+    if ((rc = make_map(&tm_v, v, KVH, kv_tokens))) return rc;
 
     Params p;
     p.items = (const int4*)workspace;
+    p.cu_k = cu_seqlens_k;
+    p.block_tables = block_tables;
+    p.MB = MB;
+    p.block_size = block_size;
     p.out = (__nv_bfloat16*)out;
     p.H = H;
     p.G = H / KVH;
@@ -759,11 +839,62 @@ extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const voi
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, B, (int4*)workspace, (int)cap));
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, cu_seqlens_k, block_tables ? 1 : 0, B,
+                                     (int4*)workspace, (int)cap));
     const int64_t ctas = pairs * H < (int64_t)sm_count() ? pairs * H : (int64_t)sm_count();
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;
     NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, varlen_prefill_kernel, tm_q, tm_k, tm_v, p));
     return NVLLM_B200_OK;
+}
+
+}  // namespace prefill
+
+int read_prefill_flags(int* out) {
+    NVLLM_CUDA_OK(cudaMemcpyFromSymbol(out, prefill::g_error_flag, sizeof(int)));
+    return NVLLM_B200_OK;
+}
+int clear_prefill_flags() {
+    const int zero = 0;
+    NVLLM_CUDA_OK(cudaMemcpyToSymbol(prefill::g_error_flag, &zero, sizeof(int)));
+    return NVLLM_B200_OK;
+}
+}  // namespace nvllm
+
+extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, int H, int KVH, int D) {
+    (void)H;
+    (void)KVH;
+    (void)D;
+    if (T < 0 || B < 0) return 256;
+    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 16;
+    return (n + 255) & ~size_t(255);
+}
+
+extern "C" int nvllm_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* cu_seqlens_q,
+                                         const int32_t* cu_seqlens_k, const int32_t* cu_seqlens_host, void* out,
+                                         void* workspace, size_t workspace_bytes, int64_t T, int B, int max_seqlen,
+                                         int H, int KVH, int D, float scale, void* stream) {
+    // packed keys/values lie beside the queries (k, v are [T, KVH, 128] like q): cu_seqlens_k must equal
+    // cu_seqlens_q, which the plan kernel checks on the device
+    return nvllm::prefill::launch("varlen_prefill", q, k, v, T, cu_seqlens_q, cu_seqlens_k, nullptr, 0, 0,
+                                  cu_seqlens_host, out, workspace, workspace_bytes, T, B, max_seqlen, H, KVH, D, scale,
+                                  stream);
+}
+
+extern "C" int nvllm_b200_paged_prefill(const void* q, const void* k_cache, const void* v_cache,
+                                        const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                        const int32_t* block_tables, const int32_t* cu_seqlens_q_host, void* out,
+                                        void* workspace, size_t workspace_bytes, int64_t T, int B, int max_seqlen_q,
+                                        int H, int KVH, int D, int NB, int block_size, int MB, float scale,
+                                        void* stream) {
+    using namespace nvllm;
+    if (!block_tables || MB <= 0) return fail(NVLLM_B200_EINVAL, "paged_prefill: block_tables required");
+    if (block_size <= 0 || block_size % prefill::kTileKV != 0)
+        return fail(NVLLM_B200_EUNSUPPORTED, "paged_prefill: block_size %d (must be a multiple of %d)", block_size,
+                    prefill::kTileKV);
+    if (NB <= 0) return fail(NVLLM_B200_EINVAL, "paged_prefill: NB must be positive");
+    return prefill::launch("paged_prefill", q, k_cache, v_cache, (int64_t)NB * block_size, cu_seqlens_q, cu_seqlens_k,
+                           block_tables, MB, block_size, cu_seqlens_q_host, out, workspace, workspace_bytes, T, B,
+                           max_seqlen_q, H, KVH, D, scale, stream);
 }

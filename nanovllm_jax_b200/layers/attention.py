@@ -17,7 +17,9 @@ Differences from the reference, all deliberate:
   * the caches are updated IN PLACE (the reference donates and rebinds them, :42, :470-475);
     ``store_kv_to_cache`` still returns the pair so call sites read the same;
   * a negative slot is skipped, as documented at :57-58 (the reference code writes slot 0);
-  * there is no gather fallback (:399-434): without the CUDA library every call raises.
+  * there is no gather fallback (:399-434): without the CUDA library every call raises;
+  * a prefill context that carries block_tables (a prefix-cache hit, engine/model_runner.py:311-314) attends the
+    cached prefix too, through the pages; the reference ignores the tables there (:351-364).
 """
 from __future__ import annotations
 
@@ -87,6 +89,20 @@ class Attention:
 
     def _prefill_attention(self, q, k, v, context: AttentionContext):
         batch_size = context.cu_seqlens_q.shape[0] - 1
+        if context.block_tables is not None:
+            # Prefix-cache hit: the model runner attaches the tables exactly when cu_seqlens_k > cu_seqlens_q
+            # (engine/model_runner.py:311-314).  The reference drops them here (:351-364) and attends the new tokens
+            # only; this layer reads the whole sequence, cached prefix included, from the pages (the new tokens'
+            # rows were stored by __call__ just before).
+            if self.k_cache is None or self.v_cache is None:
+                raise RuntimeError("prefill over a cached prefix needs the KV cache: call set_kv_cache first")
+            return ops.paged_prefill(q.to(self.k_cache.dtype).contiguous(), self.k_cache, self.v_cache,
+                                     context.block_tables, context.cu_seqlens_q, context.cu_seqlens_k,
+                                     context.max_seqlen_q, self.scale, self.block_size,
+                                     cu_seqlens_host=getattr(context, "cu_seqlens_host", None))
+        if context.max_seqlen_k != context.max_seqlen_q:
+            raise ValueError("cu_seqlens_k differs from cu_seqlens_q (a cached prefix) but the context carries no "
+                             "block_tables to read the prefix from")
         return variable_length_attention_prefill(
             q=q, k=k, v=v, cu_seqlens_q=context.cu_seqlens_q, cu_seqlens_k=context.cu_seqlens_k,
             max_seqlen_q=context.max_seqlen_q, max_seqlen_k=context.max_seqlen_k, num_heads=self.num_heads,

@@ -194,3 +194,45 @@ def varlen_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens
             _stream_ptr(q.device)))
     del keep
     return out
+
+
+def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                  cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_q: int, scale: float,
+                  block_size: int, out: torch.Tensor | None = None, cu_seqlens_host=None) -> torch.Tensor:
+    """Causal attention of packed new tokens over their whole sequences (cached prefix included), keys/values read from
+    the paged cache [NB, block, KVH, D] through ``block_tables``; returns [T, H, D] bf16.  The new tokens' K/V rows
+    must already be in the cache."""
+    _need(q, "q", torch.bfloat16, 3)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    _need(block_tables, "block_tables", torch.int32, 2)
+    _need(cu_seqlens_q, "cu_seqlens_q", torch.int32, 1)
+    _need(cu_seqlens_k, "cu_seqlens_k", torch.int32, 1)
+    t, h, d = q.shape
+    nb, blk, kvh, d2 = k_cache.shape
+    if v_cache.shape != k_cache.shape or d2 != d or blk != block_size:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} inconsistent with q {tuple(q.shape)} / block {block_size}")
+    b = cu_seqlens_q.shape[0] - 1
+    if cu_seqlens_k.shape[0] != b + 1 or block_tables.shape[0] != b:
+        raise ValueError("cu_seqlens_k / block_tables batch mismatch")
+    if out is None:
+        out = torch.empty_like(q)
+    host_ptr, keep = None, None
+    if cu_seqlens_host is not None:
+        keep = torch.as_tensor(cu_seqlens_host, dtype=torch.int32, device="cpu").contiguous()
+        if keep.shape[0] != b + 1:
+            raise ValueError("cu_seqlens_host length mismatch")
+        host_ptr = keep.data_ptr()
+        covered = int(keep[-1])
+        if 0 <= covered < t:
+            out[covered:].zero_()
+    with torch.cuda.device(q.device):
+        lib = _lib.load()
+        need = int(lib.nvllm_b200_varlen_prefill_workspace_bytes(t, b, h, kvh, d))
+        scratch = workspace(q.device, max(need, 256))
+        _lib.check(lib.nvllm_b200_paged_prefill(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(),
+            block_tables.data_ptr(), host_ptr, out.data_ptr(), scratch.data_ptr(), scratch.numel(), t, b,
+            int(max_seqlen_q), h, kvh, d, nb, block_size, block_tables.shape[1], float(scale), _stream_ptr(q.device)))
+    del keep
+    return out

@@ -243,6 +243,59 @@ def variable_length_attention_prefill(q, k, v, cu_seqlens_q, cu_seqlens_k, max_s
 
 
 # --------------------------------------------------------------------------
+# Prefix-cached prefill: the definition the reference's metadata implies
+# --------------------------------------------------------------------------
+
+
+def prefix_cached_prefill_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, cu_seqlens_k, scale, block_size):
+    """Causal attention of new query tokens over a sequence whose first tokens are already cached.
+
+    The reference has NO correct function to restate for this case: on a prefix-cache hit its model runner emits
+    cu_seqlens_k > cu_seqlens_q and attaches block tables (engine/model_runner.py:286-292, 311-314), but
+    Attention._prefill_attention ignores the tables (layers/attention.py:351-364) and masks with positions relative to
+    the new tokens (:232-236), which attends the wrong keys.  This function is therefore derived, not restated:
+      * the keys/values of sequence b are the first len_k = cu_k[b+1]-cu_k[b] tokens of the pages block_tables[b, :]
+        (the layout the model runner builds, engine/model_runner.py:300-314; the step's new K/V rows have been
+        stored first, as Attention.__call__ does at layers/attention.py:465-467);
+      * its len_q = cu_q[b+1]-cu_q[b] queries are the LAST len_q of those positions: query i sits at absolute
+        position prefix + i with prefix = len_k - len_q (engine/model_runner.py:286-292: the uncached suffix);
+      * query at position p attends keys 0..p, fp32 softmax, same GQA grouping as the decode path
+        (layers/pallas_attention.py:197-198).
+    With prefix = 0 it equals variable_length_attention_prefill on the same keys.
+
+    q : [T, H, D] fp32; k_cache, v_cache : [NB, blk, KVH, D] fp32; returns fp32 [T, H, D].
+    """
+    q = np.asarray(q, dtype=np.float32)
+    cu_q = np.asarray(cu_seqlens_q, dtype=np.int64)
+    cu_k = np.asarray(cu_seqlens_k, dtype=np.int64)
+    total, h, d = q.shape
+    kvh = k_cache.shape[2]
+    g = h // kvh
+    out = np.zeros_like(q)
+    for b in range(len(cu_q) - 1):
+        q0, lq = int(cu_q[b]), int(cu_q[b + 1] - cu_q[b])
+        lk = int(cu_k[b + 1] - cu_k[b])
+        if lq <= 0:
+            continue
+        assert lk >= lq, "a sequence cannot have fewer keys than queries"
+        prefix = lk - lq
+        nblk = -(-lk // block_size)
+        pages = np.asarray(block_tables[b][:nblk], dtype=np.int64)
+        kb = np.asarray(k_cache[pages], dtype=np.float32).reshape(nblk * block_size, kvh, d)[:lk]
+        vb = np.asarray(v_cache[pages], dtype=np.float32).reshape(nblk * block_size, kvh, d)[:lk]
+        qb = q[q0:q0 + lq].reshape(lq, kvh, g, d)
+        causal = (prefix + np.arange(lq))[:, None] >= np.arange(lk)[None, :]
+        for kh in range(kvh):
+            s = np.einsum("qgd,sd->gqs", qb[:, kh], kb[:, kh], optimize=True).astype(np.float32) * np.float32(scale)
+            s = np.where(causal[None], s, np.float32(-np.inf))
+            smax = s.max(axis=-1, keepdims=True)
+            e = np.exp(s - smax)
+            w = e / e.sum(axis=-1, keepdims=True, dtype=np.float32)
+            out[q0:q0 + lq, kh * g:(kh + 1) * g] = np.einsum("gqs,sd->qgd", w, vb[:, kh], optimize=True)
+    return out
+
+
+# --------------------------------------------------------------------------
 # Metadata exactly as the model runner builds it
 # --------------------------------------------------------------------------
 

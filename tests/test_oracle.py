@@ -190,3 +190,34 @@ def test_workload_generators_are_seeded_and_consistent():
     w4 = workloads.config4()
     assert w4.batch == 16 and w4.cu_seqlens[-1] == w4.seq_lens.sum() == w4.slot_mapping.shape[0]
     assert np.array_equal(w4.slot_mapping, ref.prefill_slot_mapping(w4.block_lists, w4.seq_lens, 256))
+
+
+def test_prefix_cached_prefill_is_the_tail_of_a_full_causal_prefill():
+    """The derived definition (oracle.prefix_cached_prefill_attention): the new tokens' rows must equal the LAST rows
+    of a plain causal prefill over the whole sequence (restated reference function, cu_q == cu_k), whatever the
+    split between cached and new tokens; with no prefix it is that function."""
+    rng = np.random.Generator(np.random.PCG64(77))
+    h, kvh, blk = 4, 2, 16
+    lens_k, prefixes = [40, 17, 64, 5], [0, 16, 33, 4]
+    nb = sum(-(-n // blk) for n in lens_k) + 2
+    kc = rng.standard_normal((nb, blk, kvh, 8), dtype=np.float32)
+    vc = rng.standard_normal((nb, blk, kvh, 8), dtype=np.float32)
+    pool = rng.permutation(nb)
+    tables = np.full((4, 5), -1, np.int32)
+    pos = 0
+    for b, n in enumerate(lens_k):
+        m = -(-n // blk)
+        tables[b, :m] = pool[pos:pos + m]
+        pos += m
+    # the whole sequences, packed, and their full causal prefill
+    k_full = np.concatenate([kc[tables[b, :-(-n // blk)]].reshape(-1, kvh, 8)[:n] for b, n in enumerate(lens_k)])
+    v_full = np.concatenate([vc[tables[b, :-(-n // blk)]].reshape(-1, kvh, 8)[:n] for b, n in enumerate(lens_k)])
+    q_full = rng.standard_normal((sum(lens_k), h, 8), dtype=np.float32)
+    cu_k = np.concatenate([[0], np.cumsum(lens_k)]).astype(np.int32)
+    full = ref.variable_length_attention_prefill(q_full, k_full, v_full, cu_k, cu_k, 1 << 30, 1 << 30, h, kvh, 0.3, 4)
+    new_lens = [n - p for n, p in zip(lens_k, prefixes)]
+    cu_q = np.concatenate([[0], np.cumsum(new_lens)]).astype(np.int32)
+    q_new = np.concatenate([q_full[cu_k[b] + prefixes[b]: cu_k[b + 1]] for b in range(4)])
+    got = ref.prefix_cached_prefill_attention(q_new, kc, vc, tables, cu_q, cu_k, 0.3, blk)
+    want = np.concatenate([full[cu_k[b] + prefixes[b]: cu_k[b + 1]] for b in range(4)])
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
