@@ -236,6 +236,47 @@ int nvllm_b200_paged_prefill(const void* q, const void* k_cache, const void* v_c
                              int NB, int block_size, int MB, float scale, void* stream);
 
 /*
+ * qk_norm_rope_store: the step a Qwen3 layer runs between its QKV projection and
+ * attention, fused into one pass over q, k, v (models/qwen3.py:157-166):
+ *     q = q_norm(q); k = k_norm(k)          layers/layernorm.py:31-48 (RMSNorm over head_dim)
+ *     q, k = rotary_emb(positions, q, k)    layers/rotary_embedding.py:13-37, 97-104
+ *     store_kv_to_cache(k, v, ...)          layers/attention.py:42-77 (called at :465-467)
+ * q and k are updated IN PLACE; the rotated k rows and the v rows are also written to
+ * their cache slots (same slot rules as nvllm_b200_store_kvcache).
+ *
+ *   q [T, H, D], k [T, KVH, D], v [T, KVH, D]  bf16
+ *   q_weight, k_weight  [D] fp32 (the RMSNorm scales); eps as layers/layernorm.py:27
+ *   cos_sin_cache  [max_pos, D] fp32: cos (D/2) | sin (D/2) per position, the table of
+ *                  layers/rotary_embedding.py:57-75; positions [T] int32, clamped to
+ *                  [0, max_pos - 1]
+ *
+ * Arithmetic: RMSNorm in fp32, rounded to bf16 (the norm returns its input dtype, :47);
+ * rotation in fp32 with separate multiplies and adds, rounded to bf16.  The sum of
+ * squares is taken in one fixed order (documented in csrc/pre_attention.cuh), so a host
+ * restatement reproduces every bf16 bit.
+ */
+int nvllm_b200_qk_norm_rope_store(void* q, void* k, const void* v, const float* q_weight, const float* k_weight,
+                                  const float* cos_sin_cache, const int32_t* positions, void* k_cache, void* v_cache,
+                                  const int32_t* slot_mapping, int64_t T, int H, int KVH, int D,
+                                  int64_t num_slots, int64_t max_pos, float eps, void* stream);
+
+/*
+ * fused_decode_step: nvllm_b200_qk_norm_rope_store (T = B) followed by
+ * nvllm_b200_paged_decode, in one C call and two kernel launches: everything a Qwen3
+ * layer does between its QKV projection and its output projection in the decode phase
+ * (models/qwen3.py:157-166 with layers/attention.py:436-480).  Argument meanings,
+ * limits and workspace size are those of the two functions; q is rotated in place and
+ * `out` receives the attention result.
+ */
+int nvllm_b200_fused_decode_step(void* q, void* k, const void* v, const float* q_weight, const float* k_weight,
+                                 const float* cos_sin_cache, const int32_t* positions, int64_t max_pos, float eps,
+                                 void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                                 const int32_t* block_tables, const int32_t* context_lens, void* out,
+                                 void* workspace, size_t workspace_bytes,
+                                 int B, int H, int KVH, int D, int NB, int block_size, int MB,
+                                 float scale, void* stream);
+
+/*
  * Clears the device-side error flags of the current device (see
  * nvllm_b200_device_status).  A host that has read and handled a non-zero status
  * calls this before it goes on.  Synchronises with the device.

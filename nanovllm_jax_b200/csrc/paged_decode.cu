@@ -21,10 +21,11 @@
 //    q.K^T and P.V; the online softmax (exp2 domain) lives in registers with
 //    warp-shuffle row reductions.
 //  * A range that ends inside a sequence leaves an fp32 partial (m, l, O) in
-//    the caller's workspace and takes a ticket for that (sequence, kv head); the
-//    CTA that draws the last ticket combines all partials of the sequence, in
-//    group order (bitwise reproducible whichever CTA arrives last), and writes
-//    the rows.  Nobody waits for anybody.  Sequences wholly inside one range are
+//    the caller's workspace; a sixth warp of the CTA (the "merger") then takes a
+//    ticket for that (sequence, kv head), and the CTA whose merger draws the last
+//    ticket combines all partials of the sequence, in group order (bitwise
+//    reproducible whichever CTA arrives last), and writes the rows.  Nobody waits
+//    for another CTA, and the warps that stream never wait for the combine.  Sequences wholly inside one range are
 //    written directly.  The tickets are cleared by the small kernel that runs
 //    before this one (decode_prepare_kernel, which in the fused decode step
 //    also scatters the step's new K/V rows into the cache).
@@ -32,6 +33,7 @@
 // No spin-wait is unbounded: every mbarrier wait gives up after a poll limit,
 // raises a device error flag (readable through nvllm_b200_device_status) and
 // the CTA drains and returns.
+#include "pre_attention.cuh"
 #include "store_kvcache.cuh"
 
 #include <mutex>
@@ -43,7 +45,8 @@ namespace decode {
 constexpr int kTile = 64;                      // tokens per tile
 constexpr int kD = 128;                        // head_dim
 constexpr int kConsumerWarps = 4;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kWarps = kConsumerWarps + 2;     // consumers, TMA producer, merger
+constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
 constexpr int kPanelBytes = kTile * 128;       // 64 tokens x 64 dims bf16, 128B-swizzled
@@ -120,43 +123,45 @@ __device__ __forceinline__ int next_item(Walk& w, const Params& p, int max_ctx, 
 }
 
 // Combine the partials of sequence b (tiles [first, first + tb) of the per-head tile stream) for kv head kvh and
-// write its G output rows; thread d of the 128 callers owns output dim d.  Partials are read in group order and
-// four at a time, so the result does not depend on which CTA runs this.
+// write its G output rows.  One warp; lane l owns output dims 4l .. 4l+3.  Partials are accumulated in group
+// order against the final row maximum, so the result does not depend on which CTA runs this.
 __device__ __forceinline__ void merge_sequence(const Params& p, int b, int kvh, long long first, int tb,
-                                               long long total, int d) {
+                                               long long total, int lane) {
     const int ng = p.num_groups;
     long long gf = ((first + 1) * ng - 1) / total;
     long long gl = ((first + tb) * ng - 1) / total;
     if (gf > ng - 1) gf = ng - 1;
     if (gl > ng - 1) gl = ng - 1;
     const size_t pf = partial_floats(p.G);
+    auto part_of = [&](long long g) { return p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf; };
+    auto live = [&](long long g) { return g * total / ng < (g + 1) * total / ng; };  // empty groups wrote nothing
     for (int r = 0; r < p.G; ++r) {
-        float mt = -INFINITY, acc = 0.f, lt = 0.f;
-        for (long long g0 = gf; g0 <= gl; g0 += 4) {
-            float mv[4], lv[4], ov[4];
+        float mt = -INFINITY;
+        for (long long g = gf + lane; g <= gl; g += 32)
+            if (live(g)) mt = fmaxf(mt, __ldcg(part_of(g) + p.G * kD + r));
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const long long g = g0 + u;
-                const bool live = g <= gl && (g * total / ng < (g + 1) * total / ng);  // skip empty groups
-                const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf;
-                mv[u] = live ? __ldcg(part + p.G * kD + r) : -INFINITY;
-                lv[u] = live ? __ldcg(part + p.G * kD + kMaxG + r) : 0.f;
-                ov[u] = live ? __ldcg(part + r * kD + d) : 0.f;
-            }
-            const float mnew = fmaxf(fmaxf(mt, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
-            if (mnew == -INFINITY) continue;
-            const float sc = (mt == -INFINITY) ? 0.f : fast_exp2(mt - mnew);
-            acc *= sc;
-            lt *= sc;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float f = (mv[u] == -INFINITY) ? 0.f : fast_exp2(mv[u] - mnew);
-                acc += ov[u] * f;
-                lt += lv[u] * f;
-            }
-            mt = mnew;
+        for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float lt = 0.f;
+#pragma unroll 4
+        for (long long g = gf; g <= gl; ++g) {
+            if (!live(g)) continue;
+            const float* part = part_of(g);
+            const float m = __ldcg(part + p.G * kD + r);
+            const float l = __ldcg(part + p.G * kD + kMaxG + r);
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(part + r * kD) + lane);
+            const float f = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+            acc.x += o.x * f;
+            acc.y += o.y * f;
+            acc.z += o.z * f;
+            acc.w += o.w * f;
+            lt += l * f;
         }
-        p.out[((size_t)b * p.H + (size_t)kvh * p.G + r) * kD + d] = __float2bfloat16_rn(acc / (lt + 1e-9f));
+        const float inv = 1.0f / (lt + 1e-9f);
+        uint2 w;
+        w.x = pack_bf16(acc.x * inv, acc.y * inv);
+        w.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G + r) * kD + 4 * lane) = w;
     }
 }
 
@@ -169,6 +174,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     uint8_t* misc = smem + kStages * kStageBytes + kOsBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);            // [kStages]
     uint64_t* empty_bar = full_bar + kStages;                          // [kStages]
+    uint64_t* part_bar = empty_bar + kStages;                          // [2]: "a partial of this CTA is in global memory"
     int* sm_i = reinterpret_cast<int*>(misc + 64);                     // scan scratch [8] + start [2] + abort [1]
     volatile int* sm_abort = sm_i + 12;
     float* sm_ml = reinterpret_cast<float*>(misc + 128);               // [2 parities][m|l][4 warps][8 rows]
@@ -184,6 +190,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_init(full_bar + s, 1);
             mbar_init(empty_bar + s, kConsumerWarps);
         }
+        mbar_init(part_bar, kConsumerWarps);
+        mbar_init(part_bar + 1, kConsumerWarps);
         fence_mbar_init();
         sm_i[10] = -1;
         sm_i[11] = 0;
@@ -198,7 +206,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     griddep_launch_dependents();  // lets the next kernel of the stream run its own prologue while this grid streams
 
     // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
-    // Every CTA scans context_lens itself (B / 160 values per thread and one warp scan): that is one global
+    // Every CTA scans context_lens itself (B / 192 values per thread and one warp scan): that is one global
     // load latency, paid in parallel by all CTAs, and cheaper than fetching the result of a serial plan.
     const int per = (p.B + kThreads - 1) / kThreads;
     const int b_lo = min(p.B, tid * per), b_hi = min(p.B, b_lo + per);
@@ -223,7 +231,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     long long total = 0;
     int warp_off = 0;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps + 1; ++w) {
+    for (int w = 0; w < kWarps; ++w) {
         const int v = sm_i[w];
         if (w < warp) warp_off += v;
         total += v;
@@ -296,6 +304,39 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         return;
     }
 
+    if (warp == kConsumerWarps + 1) {
+        // ============================== merger warp ==============================
+        // Walks the same items as the consumers.  For every item that covers only part of its sequence it waits
+        // until the consumers have put the partial into global memory, publishes it (fence + ticket) and, if this
+        // was the last partial of the sequence, combines them all.  The consumers go on streaming meanwhile.
+        uint32_t npart = 0;
+        int ctx, tb, n;
+        while ((n = next_item(walk, p, max_ctx, ctx, tb)) > 0) {
+            if (!(walk.t == 0 && walk.t + n == tb)) {
+                bool ok = true;
+                if (lane == 0) ok = !*sm_abort && mbar_wait(part_bar + (npart & 1u), (npart >> 1) & 1u);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;  // the consumers gave up (they raise the error flag) or never delivered
+                ++npart;
+                __threadfence();  // the consumers' stores, ordered before this by the barrier, become visible GPU-wide
+                unsigned int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
+                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
+                if (total >= p.num_groups)
+                    parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
+                if ((long long)ticket == parts - 1) {
+                    __threadfence();
+                    merge_sequence(p, walk.b, kvh, first, tb, total, lane);
+                }
+            }
+            walk.left -= n;
+            walk.t += n;
+        }
+        return;
+    }
+
     // ============================= consumer warps =============================
     const int row = lane >> 2;       // query head within the group (valid if < G)
     const int quad = lane & 3;
@@ -303,7 +344,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int r8 = lane & 7;
     const int tok_base = warp * 16;
     const int ctid = tid;            // 0..127 among consumers
-    uint32_t it = 0, item = 0;
+    uint32_t it = 0, item = 0, npart = 0;
     int ctx, tb, n;
     bool ok = true;
 
@@ -467,20 +508,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 }
             }
             if (!full_item) {
-                // Publish the partial, then take a ticket for this (sequence, kv head).  Whoever draws the last
-                // ticket finds every partial of the sequence visible and combines them; nobody waits.
-                __threadfence();
-                named_barrier_sync(1, kConsumerWarps * 32);
-                if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
-                named_barrier_sync(1, kConsumerWarps * 32);
-                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
-                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
-                if (total >= p.num_groups)
-                    parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
-                if ((long long)sm_i[9] == parts - 1) {
-                    __threadfence();
-                    merge_sequence(p, walk.b, kvh, first, tb, total, ctid);
-                }
+                // hand the partial to the merger warp (its fence and ticket make it visible to other CTAs)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(part_bar + (npart & 1u));
+                ++npart;
             }
         }
         walk.left -= n;
@@ -507,6 +538,20 @@ decode_prepare_kernel(unsigned int* __restrict__ tickets, int num_tickets, int s
         store_block<SrcT>(blockIdx.x, k, v, k_cache, v_cache, slot_mapping, total_chunks, row_chunks, num_slots);
     } else {
         const int i = ((int)blockIdx.x - store_blocks) * kStoreThreads + threadIdx.x;
+        if (i < num_tickets) tickets[i] = 0u;
+    }
+}
+
+// The same with the whole pre-attention step in front: blocks [0, pre_blocks) normalise and rotate the step's q and
+// k rows and scatter the k and v rows (pre_attention.cuh), the rest clear the tickets.
+__global__ void __launch_bounds__(preattn::kThreads)
+decode_prepare_fused_kernel(unsigned int* __restrict__ tickets, int num_tickets, int pre_blocks, const preattn::Params pp) {
+    griddep_wait();
+    griddep_launch_dependents();
+    if ((int)blockIdx.x < pre_blocks) {
+        preattn::pre_attention_block(blockIdx.x, pp);
+    } else {
+        const int i = ((int)blockIdx.x - pre_blocks) * preattn::kThreads + threadIdx.x;
         if (i < num_tickets) tickets[i] = 0u;
     }
 }
@@ -623,7 +668,7 @@ static int check_decode_pointers(const char* who, const DecodeArgs& a) {
 }
 
 static int launch_decode(const char* who, const DecodeArgs& a, const StepArgs* step, unsigned int* tickets,
-                         float* partials) {
+                         float* partials, const preattn::Params* pre = nullptr) {
     int rc = ensure_smem_attr();
     if (rc) return rc;
     CUtensorMap tm_k, tm_v;
@@ -665,7 +710,12 @@ static int launch_decode(const char* who, const DecodeArgs& a, const StepArgs* s
     cfg.gridDim = dim3((unsigned)(store_blocks + clear_blocks));
     cfg.blockDim = dim3(kStoreThreads);
     cfg.dynamicSmemBytes = 0;
-    if (step && step->src_dtype == NVLLM_B200_DTYPE_F32) {
+    if (pre) {
+        const int64_t pre_blocks = preattn::blocks_for(pre->T, pre->H, pre->KVH);
+        cfg.gridDim = dim3((unsigned)(pre_blocks + clear_blocks));
+        cfg.blockDim = dim3(preattn::kThreads);
+        NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_prepare_fused_kernel, tickets, num_tickets, (int)pre_blocks, *pre));
+    } else if (step && step->src_dtype == NVLLM_B200_DTYPE_F32) {
         NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_prepare_kernel<float>, tickets, num_tickets, (int)store_blocks,
                                          (const float*)step->k, (const float*)step->v, (__nv_bfloat16*)a.k_cache,
                                          (__nv_bfloat16*)a.v_cache, step->slot_mapping, total_chunks, row_chunks,
@@ -685,7 +735,7 @@ static int launch_decode(const char* who, const DecodeArgs& a, const StepArgs* s
 }
 
 static int decode_with_workspace(const char* who, const DecodeArgs& a, const StepArgs* step, void* workspace,
-                                 size_t workspace_bytes) {
+                                 size_t workspace_bytes, const preattn::Params* pre = nullptr) {
     int rc = check_decode_args(who, a);
     if (rc) return rc;
     if (step) {
@@ -704,7 +754,7 @@ static int decode_with_workspace(const char* who, const DecodeArgs& a, const Ste
         return fail(NVLLM_B200_EWORKSPACE, "%s: workspace of %zu bytes (256-byte aligned) required, got %zu", who, need,
                     workspace ? workspace_bytes : (size_t)0);
     return launch_decode(who, a, step, (unsigned int*)workspace,
-                         (float*)((uint8_t*)workspace + ticket_bytes(a.B, a.KVH)));
+                         (float*)((uint8_t*)workspace + ticket_bytes(a.B, a.KVH)), pre);
 }
 
 }  // namespace decode
@@ -739,6 +789,34 @@ extern "C" int nvllm_b200_decode_step(const void* q, const void* k, const void* 
                           stream};
     const StepArgs s = {k, v, slot_mapping, src_dtype};
     return decode_with_workspace("decode_step", a, &s, workspace, workspace_bytes);
+}
+
+namespace nvllm {
+namespace preattn {
+int check_args(const char* who, const void* q, const void* k, const void* v, const float* q_weight, const float* k_weight,
+               const float* cos_sin_cache, const int32_t* positions, const void* k_cache, const void* v_cache,
+               const int32_t* slot_mapping, int64_t T, int H, int KVH, int D, int64_t num_slots, int64_t max_pos);
+}
+}  // namespace nvllm
+
+extern "C" int nvllm_b200_fused_decode_step(void* q, void* k, const void* v, const float* q_weight, const float* k_weight,
+                                            const float* cos_sin_cache, const int32_t* positions, int64_t max_pos,
+                                            float eps, void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                                            const int32_t* block_tables, const int32_t* context_lens, void* out,
+                                            void* workspace, size_t workspace_bytes, int B, int H, int KVH, int D, int NB,
+                                            int block_size, int MB, float scale, void* stream) {
+    using namespace nvllm;
+    using namespace nvllm::decode;
+    const int64_t num_slots = (int64_t)NB * block_size;
+    int rc = preattn::check_args("fused_decode_step", q, k, v, q_weight, k_weight, cos_sin_cache, positions, k_cache, v_cache,
+                                 slot_mapping, B, H, KVH, D, num_slots, max_pos);
+    if (rc) return rc;
+    const DecodeArgs a = {q, k_cache, v_cache, block_tables, context_lens, out, B, H, KVH, D, NB, block_size, MB, scale,
+                          stream};
+    const preattn::Params pp{(__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_weight, k_weight,
+                             cos_sin_cache, positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping,
+                             (int64_t)B, H, KVH, num_slots, max_pos, eps};
+    return decode_with_workspace("fused_decode_step", a, nullptr, workspace, workspace_bytes, &pp);
 }
 
 namespace nvllm {

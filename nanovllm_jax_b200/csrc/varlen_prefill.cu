@@ -69,10 +69,9 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Params {
-    const int4* items;  // record 0: {number of (sequence, row block) pairs, 0, 0, 0}; record 1+i: {first query token of
-                        // the sequence, its query length, first row of the block, sequence index}, longest causal span
-                        // first
-    const int32_t* cu_k;          // [B+1] key offsets: packed keys = token offsets into k/v; paged = lengths only
+    const int4* items;  // record 0: {number of (sequence, row block) pairs, 0, 0, 0}; then two records per pair, longest
+                        // causal span first: {first query token of the sequence, its query length, first row of the
+                        // block, sequence index} and {first key token (packed keys), key length, 0, 0}
     const int32_t* block_tables;  // [B, MB] page ids, or nullptr for packed keys/values
     int MB, block_size;
     __nv_bfloat16* out;
@@ -276,7 +275,10 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
         for (int l = 0; l < n; ++l) {
             const int lvl = min(lvl0 + l, kMaxLevels - 1);
             const int slot = atomicAdd(&base[lvl], 1);
-            if (slot < capacity) items[1 + slot] = make_int4(start, len, l * kBlockQ, b);
+            if (slot < capacity) {
+                items[1 + 2 * slot] = make_int4(start, len, l * kBlockQ, b);
+                items[2 + 2 * slot] = make_int4(cu_k[b], len_k, 0, 0);
+            }
         }
     }
 }
@@ -313,13 +315,13 @@ __device__ __forceinline__ Item load_item(const Params& p, int idx) {
     Item it;
     const int pair = idx / p.H;
     it.head = idx - pair * p.H;
-    const int4 r = __ldg(p.items + 1 + pair);
+    const int4 r = __ldg(p.items + 1 + 2 * pair), rk = __ldg(p.items + 2 + 2 * pair);
     it.seq_start = r.x;
     it.len = r.y;
     it.q0 = r.z;
     it.b = r.w;
-    it.k_start = __ldg(p.cu_k + it.b);
-    it.len_k = __ldg(p.cu_k + it.b + 1) - it.k_start;
+    it.k_start = rk.x;
+    it.len_k = rk.y;
     it.prefix = it.len_k - it.len;  // >= 0: the plan kernel publishes no items otherwise
     const int rows = min(kBlockQ, it.len - it.q0);
     const int nk_total = (it.len_k + kTileKV - 1) / kTileKV;
@@ -820,7 +822,6 @@ static int launch(const char* who, const void* q, const void* k, const void* v, 
 
     Params p;
     p.items = (const int4*)workspace;
-    p.cu_k = cu_seqlens_k;
     p.block_tables = block_tables;
     p.MB = MB;
     p.block_size = block_size;
@@ -867,7 +868,7 @@ extern "C" size_t nvllm_b200_varlen_prefill_workspace_bytes(int64_t T, int B, in
     (void)KVH;
     (void)D;
     if (T < 0 || B < 0) return 256;
-    const size_t n = (size_t)(nvllm::prefill::item_capacity(T, B) + 1) * 16;
+    const size_t n = (size_t)(2 * nvllm::prefill::item_capacity(T, B) + 1) * 16;
     return (n + 255) & ~size_t(255);
 }
 

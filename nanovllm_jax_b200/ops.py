@@ -236,3 +236,73 @@ def paged_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
             int(max_seqlen_q), h, kvh, d, nb, block_size, block_tables.shape[1], float(scale), _stream_ptr(q.device)))
     del keep
     return out
+
+
+def _check_pre_attention(q, key, value, q_weight, k_weight, cos_sin_cache, positions, slot_mapping):
+    _need(q, "q", torch.bfloat16, 3)
+    _need(key, "key", torch.bfloat16, 3)
+    _need(value, "value", torch.bfloat16, 3)
+    _need(q_weight, "q_weight", torch.float32, 1)
+    _need(k_weight, "k_weight", torch.float32, 1)
+    _need(cos_sin_cache, "cos_sin_cache", torch.float32, 2)
+    _need(positions, "positions", torch.int32, 1)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    t, h, d = q.shape
+    if key.shape != value.shape or key.shape[0] != t or key.shape[2] != d:
+        raise ValueError(f"key/value shape {tuple(key.shape)} inconsistent with q {tuple(q.shape)}")
+    if q_weight.shape[0] != d or k_weight.shape[0] != d or cos_sin_cache.shape[1] != d:
+        raise ValueError("q_weight / k_weight / cos_sin_cache must have head_dim entries per row")
+    if positions.shape[0] != t or slot_mapping.shape[0] != t:
+        raise ValueError("positions / slot_mapping must have one entry per token")
+    return t, h, key.shape[1], d
+
+
+def qk_norm_rope_store(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, q_weight: torch.Tensor,
+                       k_weight: torch.Tensor, cos_sin_cache: torch.Tensor, positions: torch.Tensor,
+                       k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor, eps: float = 1e-6) -> None:
+    """In place, one pass: per-head RMSNorm of q and key, rotary embedding of both, scatter of the rotated key rows and
+    the value rows into the cache by slot.  Caches: any leading shape whose flattening is [num_slots, KVH, D]."""
+    t, h, kvh, d = _check_pre_attention(q, key, value, q_weight, k_weight, cos_sin_cache, positions, slot_mapping)
+    _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16)
+    if k_cache.shape != v_cache.shape or tuple(k_cache.shape[-2:]) != (kvh, d):
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} does not end in ({kvh}, {d})")
+    num_slots = k_cache.numel() // (kvh * d)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().nvllm_b200_qk_norm_rope_store(
+            q.data_ptr(), key.data_ptr(), value.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(),
+            cos_sin_cache.data_ptr(), positions.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            slot_mapping.data_ptr(), t, h, kvh, d, num_slots, cos_sin_cache.shape[0], float(eps), _stream_ptr(q.device)))
+
+
+def fused_decode_step(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, q_weight: torch.Tensor,
+                      k_weight: torch.Tensor, cos_sin_cache: torch.Tensor, positions: torch.Tensor,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                      block_tables: torch.Tensor, context_lens: torch.Tensor, scale: float, block_size: int,
+                      eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``qk_norm_rope_store`` (q and key updated in place) followed by ``paged_decode``, as one C call and two kernel
+    launches; returns the attention output [B, H, D]."""
+    b, h, kvh, d = _check_pre_attention(q, key, value, q_weight, k_weight, cos_sin_cache, positions, slot_mapping)
+    _need(k_cache, "k_cache", torch.bfloat16, 4)
+    _need(v_cache, "v_cache", torch.bfloat16, 4)
+    _need(block_tables, "block_tables", torch.int32, 2)
+    _need(context_lens, "context_lens", torch.int32, 1)
+    nb, blk, kvh2, d2 = k_cache.shape
+    if v_cache.shape != k_cache.shape or (kvh2, d2) != (kvh, d) or blk != block_size:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} inconsistent with key {tuple(key.shape)} / block {block_size}")
+    if block_tables.shape[0] != b or context_lens.shape[0] != b:
+        raise ValueError("block_tables / context_lens batch mismatch")
+    if out is None:
+        out = torch.empty_like(q)
+    with torch.cuda.device(q.device):
+        lib = _lib.load()
+        mb = block_tables.shape[1]
+        need = int(lib.nvllm_b200_paged_decode_workspace_bytes(b, h, kvh, d, mb, block_size))
+        scratch = workspace(q.device, need)
+        _lib.check(lib.nvllm_b200_fused_decode_step(
+            q.data_ptr(), key.data_ptr(), value.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(),
+            cos_sin_cache.data_ptr(), positions.data_ptr(), cos_sin_cache.shape[0], float(eps), k_cache.data_ptr(),
+            v_cache.data_ptr(), slot_mapping.data_ptr(), block_tables.data_ptr(), context_lens.data_ptr(),
+            out.data_ptr(), scratch.data_ptr(), scratch.numel(), b, h, kvh, d, nb, block_size, mb, float(scale),
+            _stream_ptr(q.device)))
+    return out

@@ -243,6 +243,67 @@ def variable_length_attention_prefill(q, k, v, cu_seqlens_q, cu_seqlens_k, max_s
 
 
 # --------------------------------------------------------------------------
+# Pre-attention step: per-head RMSNorm of q and k, rotary embedding
+# (models/qwen3.py:157-163, layers/layernorm.py:31-48, layers/rotary_embedding.py:13-37,97-104)
+# --------------------------------------------------------------------------
+
+
+def rope_cos_sin_cache(head_dim, max_position, base):
+    """The reference's table (layers/rotary_embedding.py:57-75): [max_pos, head_dim] fp32, cos(half) | sin(half)."""
+    inv_freq = (np.float32(1.0) / (np.float32(base) ** (np.arange(0, head_dim, 2, dtype=np.float32) / np.float32(head_dim))))
+    t = np.arange(max_position, dtype=np.float32)
+    freqs = (t[:, None] * inv_freq[None, :]).astype(np.float32)
+    return np.concatenate([np.cos(freqs), np.sin(freqs)], axis=-1).astype(np.float32)
+
+
+def _sum_of_squares_fixed_order(x):
+    """fp32 sum of squares over the last axis (128 elements) in ONE stated order: eight consecutive elements left to
+    right, then a butterfly over the sixteen groups (partner distance 8, 4, 2, 1).  The reference leaves the order to
+    XLA's reduction (jnp.mean, layers/layernorm.py:43); fixing one makes the bf16 results reproducible bit for bit."""
+    sq = (x * x).astype(np.float32).reshape(*x.shape[:-1], 16, 8)
+    part = sq[..., 0]
+    for i in range(1, 8):
+        part = (part + sq[..., i]).astype(np.float32)
+    idx = np.arange(16)
+    for o in (8, 4, 2, 1):
+        part = (part + part[..., idx ^ o]).astype(np.float32)
+    return part[..., 0]
+
+
+def rms_norm_heads(x_bits, weight, eps):
+    """RMSNorm over head_dim of bf16 rows (layers/layernorm.py:41-48): fp32 math, (x * rsqrt(mean(x^2) + eps)) * weight,
+    cast back to bf16.  Returns bf16 bit patterns."""
+    x = bf16_bits_to_f32(x_bits)
+    var = (_sum_of_squares_fixed_order(x) * np.float32(1.0 / x.shape[-1])).astype(np.float32)  # :43
+    inv = (np.float32(1.0) / np.sqrt((var + np.float32(eps)).astype(np.float32))).astype(np.float32)  # :44
+    y = ((x * inv[..., None]).astype(np.float32) * np.asarray(weight, np.float32)).astype(np.float32)  # :44, :47
+    return f32_to_bf16_bits(y)
+
+
+def apply_rotary_emb(x_bits, cos, sin):
+    """layers/rotary_embedding.py:31-37 on bf16 rows with the fp32 table: halves split at head_dim / 2, products and
+    sums in fp32 (bf16 * fp32 promotes), result cast to bf16 where it is consumed (the cache dtype,
+    layers/attention.py:70-71; q at :386-387).  x_bits [T, heads, D]; cos, sin [T, D/2]."""
+    x = bf16_bits_to_f32(x_bits)
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    c, s = cos[:, None, :].astype(np.float32), sin[:, None, :].astype(np.float32)
+    y1 = ((x1 * c).astype(np.float32) - (x2 * s).astype(np.float32)).astype(np.float32)
+    y2 = ((x2 * c).astype(np.float32) + (x1 * s).astype(np.float32)).astype(np.float32)
+    return f32_to_bf16_bits(np.concatenate([y1, y2], axis=-1))
+
+
+def qk_norm_rope(q_bits, k_bits, q_weight, k_weight, cos_sin_cache, positions, eps):
+    """models/qwen3.py:157-163: q_norm, k_norm, then rotary_emb(positions, q, k).  Returns (q, k) bf16 bit patterns."""
+    pos = np.clip(np.asarray(positions, np.int64), 0, cos_sin_cache.shape[0] - 1)
+    half = cos_sin_cache.shape[1] // 2
+    cos, sin = cos_sin_cache[pos, :half], cos_sin_cache[pos, half:]  # layers/rotary_embedding.py:98-101
+    qn = rms_norm_heads(q_bits, q_weight, eps)
+    kn = rms_norm_heads(k_bits, k_weight, eps)
+    return apply_rotary_emb(qn, cos, sin), apply_rotary_emb(kn, cos, sin)
+
+
+# --------------------------------------------------------------------------
 # Prefix-cached prefill: the definition the reference's metadata implies
 # --------------------------------------------------------------------------
 
