@@ -447,7 +447,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mbar_init(&sh->q_empty, 2);   // both MMA issuers
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(&sh->kv_full[s], 1);
-            mbar_init(&sh->kv_empty[s], 2);  // both MMA issuers
+            mbar_init(&sh->kv_empty[s], 3);  // both MMA issuers and the V-tile fixer
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sh->s_full[x], 1);
@@ -526,31 +526,38 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         // 0 * NaN or 0 * Inf in the P.V product would still poison the row, so this warp zeroes them in the V tile
         // once it has landed, before either MMA issuer may use it.  (Garbage in the K rows is harmless: those scores
         // are overwritten with -inf by the mask.)
-        uint32_t kt = 0, fixes = 0;
+        // The warp follows EVERY ring position in order and counts as a third reader of each slot (kv_empty expects
+        // three arrivals): a parity wait only tells the phase that completed last from the one before it, so a reader
+        // that skipped positions could mistake an older tile for the one it wants.
+        uint32_t pos = 0, fixes = 0;
         bool ok = true;
         for (int idx = first_idx; ok && idx < total; idx += stride) {
             const Item it = load_item(p, idx);
-            if (it.ragged) {
-                const uint32_t vpos = 2 * (kt + it.n_kv - 1) + 1;
+            for (int j = 0; ok && j < 2 * it.n_kv; ++j, ++pos) {
+                const int slot = pos % kSlots;
+                const bool fix = it.ragged && j == 2 * it.n_kv - 1;  // V of the last tile
                 if (lane == 0) {
-                    ok = wait_or_abort(sh, &sh->kv_full[vpos % kSlots], (vpos / kSlots) & 1u);
-                    if (ok && fixes > 0) ok = wait_or_abort(sh, &sh->fix_empty, (fixes - 1) & 1u);
+                    ok = wait_or_abort(sh, &sh->kv_full[slot], (pos / kSlots) & 1u);
+                    if (ok && fix && fixes > 0) ok = wait_or_abort(sh, &sh->fix_empty, (fixes - 1) & 1u);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                uint8_t* tile = sKV + (vpos % kSlots) * kTileBytes;
-                const int r0 = it.len_k - (it.n_kv - 1) * kTileKV;  // first row past the sequence, 1..127
-                // a row is 128 contiguous bytes in each of the two 64-dim panels (the swizzle permutes inside a row)
-                for (int i = lane; i < (kTileKV - r0) * 16; i += 32) {
-                    const int r = r0 + (i >> 4), c = i & 15;
-                    *reinterpret_cast<uint4*>(tile + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                if (fix) {
+                    uint8_t* tile = sKV + slot * kTileBytes;
+                    const int r0 = it.len_k - (it.n_kv - 1) * kTileKV;  // first row past the sequence, 1..127
+                    // a row is 128 contiguous bytes in each of the two 64-dim panels (the swizzle permutes inside a row)
+                    for (int i = lane; i < (kTileKV - r0) * 16; i += 32) {
+                        const int r = r0 + (i >> 4), c = i & 15;
+                        *reinterpret_cast<uint4*>(tile + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();  // generic-proxy writes above must be visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->fix_full);
+                    ++fixes;
                 }
-                fence_proxy_async_smem();  // generic-proxy writes above must be visible to the tensor core's reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->fix_full);
-                ++fixes;
+                if (lane == 0) mbar_arrive(&sh->kv_empty[slot]);
             }
-            kt += it.n_kv;
         }
     } else if (warp == 1 || warp == 2) {
         // ============================== MMA issuers ===============================

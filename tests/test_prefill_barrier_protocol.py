@@ -1,14 +1,15 @@
 """Event-driven CPU model of the mbarrier protocol of the prefill kernel (csrc/varlen_prefill.cu).
 
-The kernel's five roles -- TMA producer, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
-waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
+The kernel's six roles -- TMA producer, two MMA issuers, two softmax warpgroups, and the warp that zeroes the rows
+past a sequence's end in its last V tile -- only meet through mbarriers whose waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
 lists under randomised latencies and checks what the hardware cannot tell us without a hang:
 
   * no deadlock (every role runs to the end of the item list);
   * no parity alias: when a wait for phase k passes, exactly k+1 phases have completed (a barrier that got two phases
     ahead of an observer would either release it early or block it forever);
   * no barrier receives more arrivals than its count within a phase;
-  * a K/V ring slot is never refilled before both issuers have released it.
+  * a K/V ring slot is never refilled before both issuers and the V-tile fixer have released it, and the fixer never
+    touches a slot that holds another tile than the one it means.
 
 The tensor pipe is modelled as an in-order queue (a commit arrives when everything its thread issued before has
 finished), TMA loads as delayed arrivals.
@@ -99,8 +100,11 @@ class Sim:
             raise ProtocolError(f"deadlock: {sorted(self.threads)} never finished")
 
 
-def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
-    """items: per work item (n_a, n_b) = K/V tiles Q tile A / B visit (n_b = 0: no second tile)."""
+def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer_skips=False):
+    """items: per work item (n_a, n_b, ragged) = K/V tiles Q tile A / B visit (n_b = 0: no second tile) and whether the
+    last V tile reaches past the sequence's end (the fixer zeroes those rows before either issuer may use the tile).
+    fixer_skips: the broken variant in which the fixer waits only for the tiles it fixes."""
+    items = [it if len(it) == 3 else (it[0], it[1], False) for it in items]
     sim = Sim(seed, jitter)
     q_full, q_empty = Bar("q_full", 1), Bar("q_empty", 2)
     kv_full = [Bar(f"kv_full{s}", 1) for s in range(SLOTS)]
@@ -110,12 +114,14 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
     o_full = [Bar(f"o_full{x}", 1) for x in range(2)]
     o_empty = [Bar(f"o_empty{x}", 1) for x in range(2)]
     turn = [Bar(f"turn{x}", 1) for x in range(2)]
+    fix_full, fix_empty = Bar("fix_full", 1), Bar("fix_empty", 2)
+    slot_tile = [None] * SLOTS  # ring position whose tile the slot holds (or is being filled with)
     slot_state = ["empty"] * SLOTS  # ring-slot invariant: empty -> loading -> full -> (both released) -> empty
     released = [0] * SLOTS
 
     def producer():
         kt = 0
-        for i, (n_a, n_b) in enumerate(items):
+        for i, (n_a, n_b, _) in enumerate(items):
             if i > 0:
                 yield ("wait", q_empty, i - 1)
             yield ("tma", q_full)
@@ -128,21 +134,43 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                     if slot_state[s] != "empty":
                         raise ProtocolError(f"slot {s} refilled while {slot_state[s]}")
                     slot_state[s] = "full"  # (readable once kv_full completes; reads are checked against the barrier)
+                    slot_tile[s] = pos
                     yield ("tma", kv_full[s])
                 kt += 1
 
     def release(s):
         released[s] += 1
-        if released[s] == 2:
+        if released[s] == 3:
             released[s], slot_state[s] = 0, "empty"
 
+    def fixer():
+        pos = fixes = 0
+        for n_a, n_b, ragged in items:
+            n_kv = max(n_a, n_b)
+            for j in range(2 * n_kv):
+                fix = ragged and j == 2 * n_kv - 1
+                s = pos % SLOTS
+                if fix or not fixer_skips:
+                    yield ("wait", kv_full[s], pos // SLOTS)
+                if fix:
+                    if fixes > 0:
+                        yield ("wait", fix_empty, fixes - 1)
+                    if slot_tile[s] != pos:
+                        raise ProtocolError(f"fixer zeroes rows of ring position {slot_tile[s]} instead of {pos}")
+                    yield ("delay", 200)
+                    yield ("arrive", fix_full)
+                    fixes += 1
+                yield ("arrive", kv_empty[s])
+                release(s)
+                pos += 1
+
     def issuer(x):
-        kt = tiles = used = 0
+        kt = tiles = used = fixes = 0
 
         def slot(pos):
             return ("wait", kv_full[pos % SLOTS], pos // SLOTS)
 
-        for i, (n_a, n_b) in enumerate(items):
+        for i, (n_a, n_b, ragged) in enumerate(items):
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
             yield ("wait", q_full, i)
             if n_x == 0:
@@ -157,6 +185,8 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
             for j in range(n_kv):
                 vpos, kpos = 2 * (kt + j) + 1, 2 * (kt + j) + 2
                 yield slot(vpos)
+                if ragged and j == n_kv - 1:
+                    yield ("wait", fix_full, fixes)
                 if j < n_x:
                     if j == 0 and used > 0:
                         yield ("wait", o_empty[x], used - 1)
@@ -175,12 +205,15 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                     else:
                         yield ("arrive", kv_empty[kpos % SLOTS])
                     release(kpos % SLOTS)
+            if ragged:
+                yield ("arrive", fix_empty)
+                fixes += 1
             used += 1 if n_x > 0 else 0
             kt += n_kv
 
     def softmax(x):
         tiles = turns_seen = 0
-        for n_a, n_b in items:
+        for n_a, n_b, _ in items:
             n_x = (n_a, n_b)[x]
             both = n_b > 0
             for j in range(n_x):
@@ -201,6 +234,7 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                 yield ("arrive", o_empty[x])
 
     sim.spawn("producer", producer())
+    sim.spawn("fixer", fixer())
     for x in range(2):
         sim.spawn(f"issuer{x}", issuer(x))
         sim.spawn(f"softmax{x}", softmax(x))
@@ -208,9 +242,15 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
     return sim.t
 
 
-def item_tiles(q0, rows):
-    """What load_item computes for the 256-row block starting at row q0 with `rows` live rows."""
-    return q0 // 128 + 1, (q0 // 128 + 2 if rows > 128 else 0)
+def item_tiles(q0, rows, prefix=0, last=None):
+    """What load_item computes for the 256-row block starting at row q0 with `rows` live rows of a sequence with
+    `prefix` cached tokens; `last` says whether it is the sequence's final block (default: iff rows < 256)."""
+    last = rows < 256 if last is None else last
+    len_k = prefix + q0 + rows if last else prefix + q0 + rows + 300
+    nk_total = -(-len_k // 128)
+    n_a = min(nk_total, (prefix + q0 + 127) // 128 + 1)
+    n_b = min(nk_total, (prefix + q0 + 255) // 128 + 1) if rows > 128 else 0
+    return n_a, n_b, max(n_a, n_b) * 128 > len_k
 
 
 def test_single_items_of_every_shape():
@@ -222,7 +262,8 @@ def test_single_items_of_every_shape():
 @pytest.mark.parametrize("seed", range(40))
 def test_random_item_lists_under_random_latencies(seed):
     rng = random.Random(seed)
-    items = [item_tiles(256 * rng.randint(0, 7), rng.choice([1, 64, 128, 129, 200, 256, 256, 256]))
+    items = [item_tiles(256 * rng.randint(0, 7), rng.choice([1, 64, 128, 129, 200, 256, 256, 256]),
+                        prefix=rng.choice([0, 0, 1, 127, 128, 300]), last=rng.choice([None, None, True]))
              for _ in range(rng.randint(1, 14))]
     for jitter in (0.0, 0.4, 0.95):
         run_cta(items, seed=seed, jitter=jitter)
@@ -231,7 +272,11 @@ def test_random_item_lists_under_random_latencies(seed):
 def test_model_catches_broken_protocols():
     """The checker itself must report protocols that are wrong on purpose."""
     items = [item_tiles(512, 256)] * 3
-    with pytest.raises(ProtocolError):  # a ring slot released by one issuer only: refilled while the other reads it
-        run_cta(items, empty_count=1)
+    with pytest.raises(ProtocolError):  # a ring slot released before all its readers are done with it
+        run_cta(items, empty_count=2)
+    short = [(1, 0, True)] * 12  # many one-tile sequences: the fixer would run far ahead of the ring
+    with pytest.raises(ProtocolError):  # a fixer that waits only for "its" tiles mistakes an older phase for its own
+        for seed in range(20):
+            run_cta(short + items, seed=seed, jitter=0.9, fixer_skips=True)
     with pytest.raises(ProtocolError, match="deadlock"):  # tile B never hands the softmax turn back
         run_cta(items, hand_turn_back=False)
