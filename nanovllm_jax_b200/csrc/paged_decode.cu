@@ -21,11 +21,12 @@
 //    q.K^T and P.V; the online softmax (exp2 domain) lives in registers with
 //    warp-shuffle row reductions.
 //  * A range that ends inside a sequence leaves an fp32 partial (m, l, O) in
-//    the caller's workspace; a sixth warp of the CTA (the "merger") then takes a
-//    ticket for that (sequence, kv head), and the CTA whose merger draws the last
-//    ticket combines all partials of the sequence, in group order (bitwise
-//    reproducible whichever CTA arrives last), and writes the rows.  Nobody waits
-//    for another CTA, and the warps that stream never wait for the combine.  Sequences wholly inside one range are
+//    the caller's workspace and takes a ticket for that (sequence, kv head); the
+//    CTA that draws the last ticket combines all partials of the sequence, in
+//    group order (bitwise reproducible whichever CTA arrives last), and writes
+//    the rows -- all G rows at once, every load of a batch of four partials in
+//    flight together, so the combine costs about one round trip to L2 per four
+//    partials.  Nobody waits for another CTA.  Sequences wholly inside one range are
 //    written directly.  The tickets are cleared by the small kernel that runs
 //    before this one (decode_prepare_kernel, which in the fused decode step
 //    also scatters the step's new K/V rows into the cache).
@@ -45,7 +46,7 @@ namespace decode {
 constexpr int kTile = 64;                      // tokens per tile
 constexpr int kD = 128;                        // head_dim
 constexpr int kConsumerWarps = 4;
-constexpr int kWarps = kConsumerWarps + 2;     // consumers, TMA producer, merger
+constexpr int kWarps = kConsumerWarps + 1;     // consumers, TMA producer
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
@@ -123,46 +124,64 @@ __device__ __forceinline__ int next_item(Walk& w, const Params& p, int max_ctx, 
 }
 
 // Combine the partials of sequence b (tiles [first, first + tb) of the per-head tile stream) for kv head kvh and
-// write its G output rows.  One warp; lane l owns output dims 4l .. 4l+3.  Partials are accumulated in group
-// order against the final row maximum, so the result does not depend on which CTA runs this.
+// write its G output rows.  Called by the 128 consumer threads: thread t owns row t / 16 and dims 8 (t % 16) ..
+// 8 (t % 16) + 7.  Partials are taken in group order, four at a time (all loads of a batch are independent), so the
+// result does not depend on which CTA runs this.
 __device__ __forceinline__ void merge_sequence(const Params& p, int b, int kvh, long long first, int tb,
-                                               long long total, int lane) {
+                                               long long total, int ctid) {
+    const int r = ctid >> 4, c8 = (ctid & 15) * 8;
+    if (r >= p.G) return;
     const int ng = p.num_groups;
     long long gf = ((first + 1) * ng - 1) / total;
     long long gl = ((first + tb) * ng - 1) / total;
     if (gf > ng - 1) gf = ng - 1;
     if (gl > ng - 1) gl = ng - 1;
     const size_t pf = partial_floats(p.G);
-    auto part_of = [&](long long g) { return p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf; };
-    auto live = [&](long long g) { return g * total / ng < (g + 1) * total / ng; };  // empty groups wrote nothing
-    for (int r = 0; r < p.G; ++r) {
-        float mt = -INFINITY;
-        for (long long g = gf + lane; g <= gl; g += 32)
-            if (live(g)) mt = fmaxf(mt, __ldcg(part_of(g) + p.G * kD + r));
+    float mt = -INFINITY, lt = 0.f;
+    float acc[8];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float lt = 0.f;
-#pragma unroll 4
-        for (long long g = gf; g <= gl; ++g) {
-            if (!live(g)) continue;
-            const float* part = part_of(g);
-            const float m = __ldcg(part + p.G * kD + r);
-            const float l = __ldcg(part + p.G * kD + kMaxG + r);
-            const float4 o = __ldcg(reinterpret_cast<const float4*>(part + r * kD) + lane);
-            const float f = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
-            acc.x += o.x * f;
-            acc.y += o.y * f;
-            acc.z += o.z * f;
-            acc.w += o.w * f;
-            lt += l * f;
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (long long g0 = gf; g0 <= gl; g0 += 4) {
+        float mv[4], lv[4];
+        float4 oa[4], ob[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long g = g0 + u;
+            const bool live = g <= gl && (g * total / ng < (g + 1) * total / ng);  // empty groups wrote nothing
+            const float* part = p.partials + ((size_t)(g * p.KVH + kvh) * 2 + (g == gf ? 1 : 0)) * pf;
+            mv[u] = live ? __ldcg(part + p.G * kD + r) : -INFINITY;
+            lv[u] = live ? __ldcg(part + p.G * kD + kMaxG + r) : 0.f;
+            oa[u] = live ? __ldcg(reinterpret_cast<const float4*>(part + r * kD + c8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ob[u] = live ? __ldcg(reinterpret_cast<const float4*>(part + r * kD + c8) + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const float inv = 1.0f / (lt + 1e-9f);
-        uint2 w;
-        w.x = pack_bf16(acc.x * inv, acc.y * inv);
-        w.y = pack_bf16(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G + r) * kD + 4 * lane) = w;
+        const float mnew = fmaxf(fmaxf(mt, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+        if (mnew == -INFINITY) continue;
+        const float sc = (mt == -INFINITY) ? 0.f : fast_exp2(mt - mnew);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= sc;
+        lt *= sc;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float f = (mv[u] == -INFINITY) ? 0.f : fast_exp2(mv[u] - mnew);
+            acc[0] += oa[u].x * f;
+            acc[1] += oa[u].y * f;
+            acc[2] += oa[u].z * f;
+            acc[3] += oa[u].w * f;
+            acc[4] += ob[u].x * f;
+            acc[5] += ob[u].y * f;
+            acc[6] += ob[u].z * f;
+            acc[7] += ob[u].w * f;
+            lt += lv[u] * f;
+        }
+        mt = mnew;
     }
+    const float inv = 1.0f / (lt + 1e-9f);
+    uint4 w;
+    w.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    w.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    w.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+    w.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G + r) * kD + c8) = w;
 }
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
@@ -174,7 +193,6 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     uint8_t* misc = smem + kStages * kStageBytes + kOsBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);            // [kStages]
     uint64_t* empty_bar = full_bar + kStages;                          // [kStages]
-    uint64_t* part_bar = empty_bar + kStages;                          // [2]: "a partial of this CTA is in global memory"
     int* sm_i = reinterpret_cast<int*>(misc + 64);                     // scan scratch [8] + start [2] + abort [1]
     volatile int* sm_abort = sm_i + 12;
     float* sm_ml = reinterpret_cast<float*>(misc + 128);               // [2 parities][m|l][4 warps][8 rows]
@@ -190,8 +208,6 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_init(full_bar + s, 1);
             mbar_init(empty_bar + s, kConsumerWarps);
         }
-        mbar_init(part_bar, kConsumerWarps);
-        mbar_init(part_bar + 1, kConsumerWarps);
         fence_mbar_init();
         sm_i[10] = -1;
         sm_i[11] = 0;
@@ -200,13 +216,18 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         prefetch_tensormap(&tm_v);
     }
 
-    // Programmatic dependent launch: everything above overlapped the tail of the previous kernel in the
-    // stream; nothing below may touch global memory before that kernel's writes are visible.
-    griddep_wait();
     griddep_launch_dependents();  // lets the next kernel of the stream run its own prologue while this grid streams
 
+    // Programmatic dependent launch: this grid starts while the kernel launched just before it on the stream
+    // (decode_prepare_kernel: ticket clear, and in the fused step the scatter / rotation of the step's rows) is
+    // still running.  That kernel writes tickets, cache rows and (fused step) q -- never context_lens or
+    // block_tables -- and everything launched before IT has completed by the time this grid starts (its own
+    // blocks passed their griddepcontrol.wait before they let this grid go).  So the scan below and the first
+    // page lookup read only settled memory and run ahead of the wait; the wait sits right before the first
+    // access to anything the preparing kernel writes.
+
     // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
-    // Every CTA scans context_lens itself (B / 192 values per thread and one warp scan): that is one global
+    // Every CTA scans context_lens itself (B / 160 values per thread and one warp scan): that is one global
     // load latency, paid in parallel by all CTAs, and cheaper than fetching the result of a serial plan.
     const int per = (p.B + kThreads - 1) / kThreads;
     const int b_lo = min(p.B, tid * per), b_hi = min(p.B, b_lo + per);
@@ -256,6 +277,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     walk.b = sm_i[10];
     walk.t = sm_i[11];
     walk.left = x1 - x0;
+    // page of the first tile, fetched ahead of the wait (block_tables is settled memory, see above)
+    int first_phys = 0;
+    if (warp == kConsumerWarps && lane == 0)
+        first_phys = __ldg(p.block_tables + (size_t)walk.b * p.MB + (walk.t * kTile) / p.block_size);
+    griddep_wait();
 
     if (warp == kConsumerWarps) {
         // =========================== producer warp ===========================
@@ -275,7 +301,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     }
                     const int tok0 = (walk.t + i) * kTile;
                     const int bi = tok0 / p.block_size;
-                    int phys = __ldg(bt + bi);
+                    int phys = it == 0 ? first_phys : __ldg(bt + bi);
                     phys = phys < 0 ? 0 : (phys >= p.NB ? p.NB - 1 : phys);
                     const int slot = phys * p.block_size + (tok0 - bi * p.block_size);
                     uint8_t* st = smem + stage * kStageBytes;
@@ -304,39 +330,6 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         return;
     }
 
-    if (warp == kConsumerWarps + 1) {
-        // ============================== merger warp ==============================
-        // Walks the same items as the consumers.  For every item that covers only part of its sequence it waits
-        // until the consumers have put the partial into global memory, publishes it (fence + ticket) and, if this
-        // was the last partial of the sequence, combines them all.  The consumers go on streaming meanwhile.
-        uint32_t npart = 0;
-        int ctx, tb, n;
-        while ((n = next_item(walk, p, max_ctx, ctx, tb)) > 0) {
-            if (!(walk.t == 0 && walk.t + n == tb)) {
-                bool ok = true;
-                if (lane == 0) ok = !*sm_abort && mbar_wait(part_bar + (npart & 1u), (npart >> 1) & 1u);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;  // the consumers gave up (they raise the error flag) or never delivered
-                ++npart;
-                __threadfence();  // the consumers' stores, ordered before this by the barrier, become visible GPU-wide
-                unsigned int ticket = 0;
-                if (lane == 0) ticket = atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
-                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
-                if (total >= p.num_groups)
-                    parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
-                if ((long long)ticket == parts - 1) {
-                    __threadfence();
-                    merge_sequence(p, walk.b, kvh, first, tb, total, lane);
-                }
-            }
-            walk.left -= n;
-            walk.t += n;
-        }
-        return;
-    }
-
     // ============================= consumer warps =============================
     const int row = lane >> 2;       // query head within the group (valid if < G)
     const int quad = lane & 3;
@@ -344,7 +337,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int r8 = lane & 7;
     const int tok_base = warp * 16;
     const int ctid = tid;            // 0..127 among consumers
-    uint32_t it = 0, item = 0, npart = 0;
+    uint32_t it = 0, item = 0;
     int ctx, tb, n;
     bool ok = true;
 
@@ -508,10 +501,20 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 }
             }
             if (!full_item) {
-                // hand the partial to the merger warp (its fence and ticket make it visible to other CTAs)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(part_bar + (npart & 1u));
-                ++npart;
+                // Publish the partial, then take a ticket for this (sequence, kv head).  Whoever draws the last
+                // ticket finds every partial of the sequence visible and combines them; nobody waits.
+                __threadfence();
+                named_barrier_sync(1, kConsumerWarps * 32);
+                if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
+                named_barrier_sync(1, kConsumerWarps * 32);
+                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
+                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
+                if (total >= p.num_groups)
+                    parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
+                if ((long long)sm_i[9] == parts - 1) {
+                    __threadfence();
+                    merge_sequence(p, walk.b, kvh, first, tb, total, ctid);
+                }
             }
         }
         walk.left -= n;

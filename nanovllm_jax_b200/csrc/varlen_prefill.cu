@@ -291,7 +291,6 @@ struct Shared {
     uint64_t kv_full[kSlots], kv_empty[kSlots];
     uint64_t s_full[2], p_full[2][2], o_full[2], o_empty[2];
     uint64_t turn[2];  // softmax ping-pong: turn[0] = "tile A finished a softmax", turn[1] = "tile B finished one"
-    uint64_t fix_full, fix_empty;  // last V tile of a sequence: rows past the sequence's end have been zeroed / used
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -447,7 +446,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mbar_init(&sh->q_empty, 2);   // both MMA issuers
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(&sh->kv_full[s], 1);
-            mbar_init(&sh->kv_empty[s], 3);  // both MMA issuers and the V-tile fixer
+            mbar_init(&sh->kv_empty[s], 2);  // both MMA issuers
         }
         for (int x = 0; x < 2; ++x) {
             mbar_init(&sh->s_full[x], 1);
@@ -457,8 +456,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mbar_init(&sh->o_empty[x], kTileQ / 32);
             mbar_init(&sh->turn[x], kTileQ / 32);
         }
-        mbar_init(&sh->fix_full, 1);
-        mbar_init(&sh->fix_empty, 2);  // both MMA issuers
         sh->abort_flag = 0;
         sh->tmem_base = 0xFFFFFFFFu;
         fence_mbar_init();
@@ -519,46 +516,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
             }
         }
-    } else if (warp == 3) {
-        // ================================ V-tile fixer ================================
-        // The last KV tile of a sequence reaches past its last key: those rows of the tile hold whatever follows
-        // in memory (the next sequence, padding, recycled cache rows).  Their probabilities are exactly zero, but
-        // 0 * NaN or 0 * Inf in the P.V product would still poison the row, so this warp zeroes them in the V tile
-        // once it has landed, before either MMA issuer may use it.  (Garbage in the K rows is harmless: those scores
-        // are overwritten with -inf by the mask.)
-        // The warp follows EVERY ring position in order and counts as a third reader of each slot (kv_empty expects
-        // three arrivals): a parity wait only tells the phase that completed last from the one before it, so a reader
-        // that skipped positions could mistake an older tile for the one it wants.
-        uint32_t pos = 0, fixes = 0;
-        bool ok = true;
-        for (int idx = first_idx; ok && idx < total; idx += stride) {
-            const Item it = load_item(p, idx);
-            for (int j = 0; ok && j < 2 * it.n_kv; ++j, ++pos) {
-                const int slot = pos % kSlots;
-                const bool fix = it.ragged && j == 2 * it.n_kv - 1;  // V of the last tile
-                if (lane == 0) {
-                    ok = wait_or_abort(sh, &sh->kv_full[slot], (pos / kSlots) & 1u);
-                    if (ok && fix && fixes > 0) ok = wait_or_abort(sh, &sh->fix_empty, (fixes - 1) & 1u);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                if (fix) {
-                    uint8_t* tile = sKV + slot * kTileBytes;
-                    const int r0 = it.len_k - (it.n_kv - 1) * kTileKV;  // first row past the sequence, 1..127
-                    // a row is 128 contiguous bytes in each of the two 64-dim panels (the swizzle permutes inside a row)
-                    for (int i = lane; i < (kTileKV - r0) * 16; i += 32) {
-                        const int r = r0 + (i >> 4), c = i & 15;
-                        *reinterpret_cast<uint4*>(tile + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) =
-                            make_uint4(0, 0, 0, 0);
-                    }
-                    fence_proxy_async_smem();  // generic-proxy writes above must be visible to the tensor core's reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->fix_full);
-                    ++fixes;
-                }
-                if (lane == 0) mbar_arrive(&sh->kv_empty[slot]);
-            }
-        }
     } else if (warp == 1 || warp == 2) {
         // ============================== MMA issuers ===============================
         // One issuing thread per Q tile (warp 1: tile A, warp 2: tile B).  An issuing thread blocks on every
@@ -578,7 +535,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             uint32_t kt = 0;     // K/V tiles consumed before this item
             uint32_t tiles = 0;  // tiles finished by this Q tile, over all items (barrier phases)
             uint32_t used = 0;   // items in which this Q tile was active (o_empty phases)
-            uint32_t fixes = 0;  // sequence-final items seen (fix_full / fix_empty phases)
             int i = 0;
             bool ok = true;
 
@@ -627,11 +583,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int j = 0; ok && j < it.n_kv; ++j) {
                     const uint32_t vpos = 2 * (kt + j) + 1, kpos = vpos + 1;  // ring positions of V(j) and K(j+1)
                     if (!(ok = slot_full(vpos))) break;
-                    if (it.ragged && j == it.n_kv - 1) {
-                        // the fixer has zeroed the rows past the sequence's end; the slot is released only after this
-                        if (!(ok = wait_or_abort(sh, &sh->fix_full, fixes & 1u))) break;
-                        tc_fence_after();
-                    }
                     if (j < n_x) {
                         if (!(ok = issue_pv(j, v_desc0 + (vpos % kSlots) * kSlotStep))) break;
                         tc_commit(&sh->kv_empty[vpos % kSlots]);
@@ -649,10 +600,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                             mbar_arrive(&sh->kv_empty[kpos % kSlots]);
                         }
                     }
-                }
-                if (it.ragged) {
-                    mbar_arrive(&sh->fix_empty);
-                    ++fixes;
                 }
                 used += n_x > 0 ? 1 : 0;
                 kt += it.n_kv;
@@ -674,10 +621,13 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         // queue up behind one another.  Inside an item with both tiles active the softmaxes therefore alternate
         // A(0) B(0) A(1) B(1) ..., so that one tile's MMAs run under the other tile's softmax.
         uint32_t turns_seen = 0;  // completions of the other tile's turn barrier this warp has consumed
+        uint32_t kt = 0;          // K/V tiles of the items before this one (ring positions)
         bool ok = true;
         for (int idx = first_idx; ok && idx < total; idx += stride) {
             const Item it = load_item(p, idx);
             const int n_x = x == 0 ? it.n_a : it.n_b;
+            const uint32_t kt0 = kt;
+            kt += it.n_kv;
             if (n_x == 0) continue;
             const bool both = it.n_b > 0;
             const int q_pos = it.q0 + x * kTileQ + row;             // row of the sequence's query block
@@ -691,6 +641,29 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     ++turns_seen;
                 }
                 tc_fence_after();
+                if (it.ragged && j == it.n_kv - 1) {
+                    // The last KV tile of the sequence reaches past its last key: those rows of the V tile hold
+                    // whatever follows in memory (the next sequence, padding, recycled cache rows).  Their
+                    // probabilities are exactly zero, but 0 * NaN or 0 * Inf in the P.V product would still poison the
+                    // row, so each thread zeroes "its" row of the V tile before this tile's P is handed over (the
+                    // hand-over orders these stores before the MMA that reads them).  Garbage in the K rows is
+                    // harmless: those scores are overwritten with -inf by the mask.  This warpgroup trails the MMA
+                    // issuer, and the slot cannot be refilled before P.V of this very tile, so the parity wait sees
+                    // either "still loading" or "landed", never another tile.  When both Q tiles use the tile both
+                    // warpgroups zero it (same bytes, same value).
+                    const uint32_t vpos = 2 * (kt0 + it.n_kv - 1) + 1;
+                    if (!(ok = wait_or_abort(sh, &sh->kv_full[vpos % kSlots], (vpos / kSlots) & 1u))) break;
+                    if (row >= it.len_k - (it.n_kv - 1) * kTileKV) {
+                        // a row is 128 contiguous bytes in each 64-dim panel (the swizzle permutes inside a row)
+                        uint8_t* vrow = sKV + (vpos % kSlots) * kTileBytes + row * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4*>(vrow + kPanelBytes + c * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                        fence_proxy_async_smem();  // generic-proxy stores must be visible to the tensor core's reads
+                    }
+                }
                 // the tile needs masking iff its last key lies beyond what the first row may see (one tile when the
                 // prefix is a multiple of the tile, two otherwise)
                 if (j * kTileKV + kTileKV - 1 > first_lim)

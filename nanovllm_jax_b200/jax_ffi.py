@@ -19,7 +19,7 @@ from . import _lib
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ADAPTER_SOURCE = os.path.join(_HERE, "csrc", "xla_ffi", "nvllm_b200_ffi.cc")
 ADAPTER_LIB = os.path.join(_HERE, "libnvllm_b200_ffi.so")
-TARGETS = ("NvllmStore", "NvllmDecode", "NvllmPrefill")
+TARGETS = ("NvllmStore", "NvllmDecode", "NvllmPrefill", "NvllmPagedPrefill", "NvllmStoreInPlace", "NvllmDecodeStepInPlace")
 
 PALLAS_AVAILABLE = True  # flag tested by the reference at layers/attention.py:384
 _registered = False
@@ -98,4 +98,64 @@ def paged_prefill_attention(q, k, v, cu_seqlens, max_seqlen: int, scale: float):
     out, _ = jax.ffi.ffi_call("NvllmPrefill", (jax.ShapeDtypeStruct(q.shape, q.dtype),
                                                jax.ShapeDtypeStruct((nbytes,), jnp.uint8)))(
         q, k, v, cu, cu, scale=np.float32(scale), max_seqlen=np.int32(max_seqlen))
+    return out
+
+
+def paged_prefill_from_cache(q, k_cache, v_cache, block_tables, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int,
+                             scale: float, block_size: int):
+    """Prefill over a cached prefix (``nvllm_b200_paged_prefill``): the branch Attention._prefill_attention takes when the
+    context carries block_tables (engine/model_runner.py:311-314).  The new tokens' K/V rows must already be stored."""
+    import numpy as np
+    jax, jnp = _jax()
+    register()
+    t, h, d = q.shape
+    nbytes = max(256, int(_lib.load().nvllm_b200_varlen_prefill_workspace_bytes(t, cu_seqlens_q.shape[0] - 1, h,
+                                                                               k_cache.shape[2], d)))
+    out, _ = jax.ffi.ffi_call("NvllmPagedPrefill", (jax.ShapeDtypeStruct(q.shape, q.dtype),
+                                                    jax.ShapeDtypeStruct((nbytes,), jnp.uint8)))(
+        q, k_cache, v_cache, cu_seqlens_q.astype(jnp.int32), cu_seqlens_k.astype(jnp.int32),
+        block_tables.astype(jnp.int32), scale=np.float32(scale), max_seqlen=np.int32(max_seqlen_q))
+    return out
+
+
+# ---- mode B: caches held outside the traced state, written through a stable device pointer ------------------------
+# The functional store above is always correct, but under the reference's outer, non-donating nnx.jit
+# (engine/model_runner.py:217-223) XLA may copy each layer's cache every step before the aliased call.  In this mode
+# the cache buffers are allocated once by the runner, stay out of the jitted function's operands, and the custom
+# calls receive their ADDRESSES as 64-bit attributes and are marked side-effecting: nothing can be copied, nothing is
+# rebound.  The buffers must outlive every executable that embeds the addresses; re-allocating the cache means
+# re-tracing.  UNVERIFIED like the rest of this module (JAX absent in the build image).
+
+def cache_address(array) -> int:
+    """Device address of a committed, single-device jax.Array (its buffer must stay alive while the address is used)."""
+    return int(array.unsafe_buffer_pointer())
+
+
+def store_kv_to_cache_side_effect(key, value, k_cache_addr: int, v_cache_addr: int, num_slots: int, slot_mapping):
+    """``store_kv_to_cache`` writing through fixed cache addresses; returns a token array the caller threads into the
+    attention call so that XLA keeps the order store -> attend."""
+    import numpy as np
+    jax, jnp = _jax()
+    register()
+    call = jax.ffi.ffi_call("NvllmStoreInPlace", jax.ShapeDtypeStruct((1,), jnp.int32), has_side_effect=True)
+    return call(key, value, slot_mapping.astype(jnp.int32), k_cache=np.int64(k_cache_addr), v_cache=np.int64(v_cache_addr),
+                num_slots=np.int64(num_slots))
+
+
+def decode_step_side_effect(q, key, value, k_cache_addr: int, v_cache_addr: int, num_blocks: int, num_kv_heads: int,
+                            slot_mapping, block_tables, context_lens, scale: float, block_size: int):
+    """Store + decode attention (``nvllm_b200_decode_step``) on caches addressed by pointer: one side-effecting call per
+    layer and decode step."""
+    import numpy as np
+    jax, jnp = _jax()
+    register()
+    b, h, d = q.shape
+    nbytes = int(_lib.load().nvllm_b200_paged_decode_workspace_bytes(b, h, num_kv_heads, d, block_tables.shape[1],
+                                                                     block_size))
+    out, _ = jax.ffi.ffi_call("NvllmDecodeStepInPlace", (jax.ShapeDtypeStruct(q.shape, q.dtype),
+                                                         jax.ShapeDtypeStruct((nbytes,), jnp.uint8)),
+                              has_side_effect=True)(
+        q, key, value, slot_mapping.astype(jnp.int32), block_tables.astype(jnp.int32), context_lens.astype(jnp.int32),
+        k_cache=np.int64(k_cache_addr), v_cache=np.int64(v_cache_addr), num_blocks=np.int32(num_blocks),
+        block_size=np.int32(block_size), scale=np.float32(scale))
     return out

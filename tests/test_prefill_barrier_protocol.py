@@ -1,15 +1,16 @@
 """Event-driven CPU model of the mbarrier protocol of the prefill kernel (csrc/varlen_prefill.cu).
 
-The kernel's six roles -- TMA producer, two MMA issuers, two softmax warpgroups, and the warp that zeroes the rows
-past a sequence's end in its last V tile -- only meet through mbarriers whose waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
+The kernel's five roles -- TMA producer, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
+waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
 lists under randomised latencies and checks what the hardware cannot tell us without a hang:
 
   * no deadlock (every role runs to the end of the item list);
   * no parity alias: when a wait for phase k passes, exactly k+1 phases have completed (a barrier that got two phases
     ahead of an observer would either release it early or block it forever);
   * no barrier receives more arrivals than its count within a phase;
-  * a K/V ring slot is never refilled before both issuers and the V-tile fixer have released it, and the fixer never
-    touches a slot that holds another tile than the one it means.
+  * a K/V ring slot is never refilled before both issuers have released it;
+  * the softmax warpgroup that zeroes the rows past a sequence's end in its last V tile waits for that slot only
+    at such tiles (skipping every other phase of the slot), and still never sees another tile there.
 
 The tensor pipe is modelled as an in-order queue (a commit arrives when everything its thread issued before has
 finished), TMA loads as delayed arrivals.
@@ -100,10 +101,9 @@ class Sim:
             raise ProtocolError(f"deadlock: {sorted(self.threads)} never finished")
 
 
-def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer_skips=False):
-    """items: per work item (n_a, n_b, ragged) = K/V tiles Q tile A / B visit (n_b = 0: no second tile) and whether the
-    last V tile reaches past the sequence's end (the fixer zeroes those rows before either issuer may use the tile).
-    fixer_skips: the broken variant in which the fixer waits only for the tiles it fixes."""
+def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
+    """items: per work item (n_a, n_b[, ragged]) = K/V tiles Q tile A / B visit (n_b = 0: no second tile) and whether
+    the last V tile reaches past the sequence's end (the softmax warpgroups that use it zero those rows first)."""
     items = [it if len(it) == 3 else (it[0], it[1], False) for it in items]
     sim = Sim(seed, jitter)
     q_full, q_empty = Bar("q_full", 1), Bar("q_empty", 2)
@@ -114,7 +114,6 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer
     o_full = [Bar(f"o_full{x}", 1) for x in range(2)]
     o_empty = [Bar(f"o_empty{x}", 1) for x in range(2)]
     turn = [Bar(f"turn{x}", 1) for x in range(2)]
-    fix_full, fix_empty = Bar("fix_full", 1), Bar("fix_empty", 2)
     slot_tile = [None] * SLOTS  # ring position whose tile the slot holds (or is being filled with)
     slot_state = ["empty"] * SLOTS  # ring-slot invariant: empty -> loading -> full -> (both released) -> empty
     released = [0] * SLOTS
@@ -140,37 +139,16 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer
 
     def release(s):
         released[s] += 1
-        if released[s] == 3:
+        if released[s] == 2:
             released[s], slot_state[s] = 0, "empty"
 
-    def fixer():
-        pos = fixes = 0
-        for n_a, n_b, ragged in items:
-            n_kv = max(n_a, n_b)
-            for j in range(2 * n_kv):
-                fix = ragged and j == 2 * n_kv - 1
-                s = pos % SLOTS
-                if fix or not fixer_skips:
-                    yield ("wait", kv_full[s], pos // SLOTS)
-                if fix:
-                    if fixes > 0:
-                        yield ("wait", fix_empty, fixes - 1)
-                    if slot_tile[s] != pos:
-                        raise ProtocolError(f"fixer zeroes rows of ring position {slot_tile[s]} instead of {pos}")
-                    yield ("delay", 200)
-                    yield ("arrive", fix_full)
-                    fixes += 1
-                yield ("arrive", kv_empty[s])
-                release(s)
-                pos += 1
-
     def issuer(x):
-        kt = tiles = used = fixes = 0
+        kt = tiles = used = 0
 
         def slot(pos):
             return ("wait", kv_full[pos % SLOTS], pos // SLOTS)
 
-        for i, (n_a, n_b, ragged) in enumerate(items):
+        for i, (n_a, n_b, _) in enumerate(items):
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
             yield ("wait", q_full, i)
             if n_x == 0:
@@ -185,8 +163,6 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer
             for j in range(n_kv):
                 vpos, kpos = 2 * (kt + j) + 1, 2 * (kt + j) + 2
                 yield slot(vpos)
-                if ragged and j == n_kv - 1:
-                    yield ("wait", fix_full, fixes)
                 if j < n_x:
                     if j == 0 and used > 0:
                         yield ("wait", o_empty[x], used - 1)
@@ -205,19 +181,23 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer
                     else:
                         yield ("arrive", kv_empty[kpos % SLOTS])
                     release(kpos % SLOTS)
-            if ragged:
-                yield ("arrive", fix_empty)
-                fixes += 1
             used += 1 if n_x > 0 else 0
             kt += n_kv
 
     def softmax(x):
-        tiles = turns_seen = 0
-        for n_a, n_b, _ in items:
-            n_x = (n_a, n_b)[x]
+        tiles = turns_seen = kt = 0
+        for n_a, n_b, ragged in items:
+            n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
+            kt0, kt = kt, kt + n_kv
             both = n_b > 0
             for j in range(n_x):
                 yield ("wait", s_full[x], tiles)
+                if ragged and j == n_kv - 1:  # zero the rows past the sequence's end in V(last) before P is handed over
+                    vpos = 2 * (kt0 + n_kv - 1) + 1
+                    yield ("wait", kv_full[vpos % SLOTS], vpos // SLOTS)
+                    if slot_tile[vpos % SLOTS] != vpos:
+                        raise ProtocolError(f"softmax{x} zeroes rows of ring position {slot_tile[vpos % SLOTS]}, not {vpos}")
+                    yield ("delay", 60)
                 if both and (j >= 1 if x == 0 else j < n_a):  # A(j) after B(j-1); B(j) after A(j) while A has tiles
                     yield ("wait", turn[x ^ 1], turns_seen)
                     turns_seen += 1
@@ -234,7 +214,6 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=3, hand_turn_back=True, fixer
                 yield ("arrive", o_empty[x])
 
     sim.spawn("producer", producer())
-    sim.spawn("fixer", fixer())
     for x in range(2):
         sim.spawn(f"issuer{x}", issuer(x))
         sim.spawn(f"softmax{x}", softmax(x))
@@ -272,11 +251,7 @@ def test_random_item_lists_under_random_latencies(seed):
 def test_model_catches_broken_protocols():
     """The checker itself must report protocols that are wrong on purpose."""
     items = [item_tiles(512, 256)] * 3
-    with pytest.raises(ProtocolError):  # a ring slot released before all its readers are done with it
-        run_cta(items, empty_count=2)
-    short = [(1, 0, True)] * 12  # many one-tile sequences: the fixer would run far ahead of the ring
-    with pytest.raises(ProtocolError):  # a fixer that waits only for "its" tiles mistakes an older phase for its own
-        for seed in range(20):
-            run_cta(short + items, seed=seed, jitter=0.9, fixer_skips=True)
+    with pytest.raises(ProtocolError):  # a ring slot released by one issuer only: refilled while the other reads it
+        run_cta(items, empty_count=1)
     with pytest.raises(ProtocolError, match="deadlock"):  # tile B never hands the softmax turn back
         run_cta(items, hand_turn_back=False)
