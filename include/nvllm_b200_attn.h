@@ -163,6 +163,7 @@ int nvllm_b200_paged_decode_static(const void* q, const void* k_cache, const voi
  * Bit 2 (4): a prefill pipeline wait timed out.  Bit 4 (16): a sequence too long
  * for the prefill plan.  Bit 5 (32): prefill called with inconsistent
  * cu_seqlens_q / cu_seqlens_k (see nvllm_b200_varlen_prefill / _paged_prefill).
+ * Bit 6 (64): an all-reduce gave up waiting for a peer's flag.
  * This call synchronises with the device (it copies one int back).
  */
 int nvllm_b200_device_status(int* flags_host);
@@ -275,6 +276,37 @@ int nvllm_b200_fused_decode_step(void* q, void* k, const void* v, const float* q
                                  void* workspace, size_t workspace_bytes,
                                  int B, int H, int KVH, int D, int NB, int block_size, int MB,
                                  float scale, void* stream);
+
+/*
+ * One-shot all-reduce (sum) over the tensor-parallel ranks of ONE node for decode-size bf16 messages, through
+ * NVLink peer memory.  Replaces the collective behind the reference's row-parallel projections
+ * (RowParallelLinear.__call__, layers/linear.py:486-510; o_proj models/qwen3.py:170, down_proj :230), optionally
+ * fused with the residual add that follows it (models/qwen3.py:225-231).
+ *
+ * Set-up (these three DO allocate / map device memory; call them once, outside the serving loop):
+ *   comm_alloc   allocates this rank's symmetric buffer (nvllm_b200_comm_buffer_bytes(max_bytes) bytes, zeroed) and
+ *                returns its 64-byte CUDA IPC handle, to be sent to the other ranks by any means;
+ *   comm_open    maps a peer's buffer from its handle; comm_close unmaps it; comm_free frees one's own.
+ * allreduce_sum: out = sum over ranks of in (+ residual), `count` bf16 elements (a multiple of 8, count*2 <= max_bytes).
+ *   buffers_host  HOST array of `world` device pointers: entry r = rank r's buffer as mapped in this process
+ *   epoch         1, 2, 3, ... : the same value on every rank for the same call, increasing by one per call
+ *   max_spins     bound of the wait for the peers' flags; when it runs out the call's kernel raises bit 6 (64) of
+ *                 nvllm_b200_device_status, leaves `out` unwritten for the affected parts and returns
+ * in, out and residual may alias one another.  Results are bit-identical on every rank (fixed summation order).
+ * Every rank must issue the same sequence of calls; calls of one communicator must not overlap on the GPU.
+ * allreduce_sum_emulated runs all ranks of a world on ONE device in one cooperative launch (single-GPU tests).
+ */
+size_t nvllm_b200_comm_buffer_bytes(size_t max_bytes);
+int nvllm_b200_comm_alloc(size_t max_bytes, void** buffer, void* ipc_handle_64);
+int nvllm_b200_comm_open(const void* ipc_handle_64, void** buffer);
+int nvllm_b200_comm_close(void* buffer);
+int nvllm_b200_comm_free(void* buffer);
+int nvllm_b200_allreduce_sum(const void* in, void* out, const void* residual, void* const* buffers_host,
+                             int rank, int world, int64_t count, size_t max_bytes, unsigned int epoch,
+                             int64_t max_spins, void* stream);
+int nvllm_b200_allreduce_sum_emulated(void* const* in, void* const* out, void* const* residual,
+                                      void* const* buffers_host, int world, int64_t count, size_t max_bytes,
+                                      unsigned int epoch, int64_t max_spins, void* stream);
 
 /*
  * Clears the device-side error flags of the current device (see

@@ -33,6 +33,13 @@ SIGNATURES = {
     "nvllm_b200_varlen_prefill": (_i32, [_vp] * 8 + [_sz, _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
     "nvllm_b200_paged_prefill": (_i32, [_vp] * 9 + [_sz, _i64] + [_i32] * 8 + [_f32, _vp]),
     "nvllm_b200_device_status_reset": (_i32, []),
+    "nvllm_b200_comm_buffer_bytes": (_sz, [_sz]),
+    "nvllm_b200_comm_alloc": (_i32, [_sz, _c.POINTER(_vp), _vp]),
+    "nvllm_b200_comm_open": (_i32, [_vp, _c.POINTER(_vp)]),
+    "nvllm_b200_comm_close": (_i32, [_vp]),
+    "nvllm_b200_comm_free": (_i32, [_vp]),
+    "nvllm_b200_allreduce_sum": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _sz, _c.c_uint, _i64, _vp]),
+    "nvllm_b200_allreduce_sum_emulated": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _sz, _c.c_uint, _i64, _vp]),
     "nvllm_b200_qk_norm_rope_store": (_i32, [_vp] * 10 + [_i64, _i32, _i32, _i32, _i64, _i64, _f32, _vp]),
     "nvllm_b200_fused_decode_step": (_i32, [_vp] * 7 + [_i64, _f32] + [_vp] * 7 + [_sz] + [_i32] * 7 + [_f32, _vp]),
 }

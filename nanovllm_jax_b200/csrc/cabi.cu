@@ -57,10 +57,11 @@ extern "C" const char* nvllm_b200_last_error_string(void) { return nvllm::last_e
 extern "C" int nvllm_b200_device_status(int* flags_host) {
     using namespace nvllm;
     if (!flags_host) return fail(NVLLM_B200_EINVAL, "device_status: null pointer");
-    int a = 0, b = 0, rc;
+    int a = 0, b = 0, c = 0, rc;
     if ((rc = read_decode_flags(&a))) return rc;
     if ((rc = read_prefill_flags(&b))) return rc;
-    *flags_host = a | b;
+    if ((rc = read_comm_flags(&c))) return rc;
+    *flags_host = a | b | c;
     return NVLLM_B200_OK;
 }
 
@@ -68,5 +69,6 @@ extern "C" int nvllm_b200_device_status_reset(void) {
     using namespace nvllm;
     int rc;
     if ((rc = clear_decode_flags())) return rc;
-    return clear_prefill_flags();
+    if ((rc = clear_prefill_flags())) return rc;
+    return clear_comm_flags();
 }

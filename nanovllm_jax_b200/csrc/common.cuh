@@ -44,8 +44,10 @@ EncodeTiledFn encode_tiled_fn();
 // Per-translation-unit device error flags (each kernel file owns one); both synchronise with the device.
 int read_decode_flags(int* out);
 int read_prefill_flags(int* out);
+int read_comm_flags(int* out);
 int clear_decode_flags();
 int clear_prefill_flags();
+int clear_comm_flags();
 
 // Programmatic dependent launch between the library's kernels is on unless NVLLM_B200_PDL=0.
 bool pdl_enabled();
