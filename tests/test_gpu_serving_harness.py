@@ -1,5 +1,5 @@
 """The serving harness (bench_serving.py) on a tiny model: tokens produced through the library's attention
-(store_kvcache + varlen prefill + paged decode, pages permuted) must be the ones a dense torch forward over the whole
+(fused or separate pre-attention step, varlen prefill, paged decode over fixed-shape metadata) must be the ones a dense torch forward over the whole
 sequence would pick (teacher-forced: at every step the harness's token must be within a whisker of the dense top logit)."""
 import os
 import sys
@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_generated_tokens_agree_with_dense_forward():
+@pytest.mark.parametrize("fused", [True, False])
+def test_generated_tokens_agree_with_dense_forward(fused):
     import torch
     import torch.nn.functional as F
     sys.path.insert(0, ROOT)
@@ -19,7 +20,7 @@ def test_generated_tokens_agree_with_dense_forward():
 
     dev = torch.device("cuda", 0)
     cfg = bs.Qwen3Config(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=128, intermediate=512, vocab=512)
-    model = bs.Qwen3(cfg, 1, 0, dev, seed=3)
+    model = bs.Qwen3(cfg, 1, 0, dev, seed=3, fused=fused)
     # larger weights so that logits are well separated
     for layer in model.layers:
         for name in ("w_qkv", "w_o", "w_gate_up", "w_down"):
