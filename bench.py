@@ -662,6 +662,12 @@ def run_b200(args):
     for i in range(max(args.warmup, 3)):
         rig.step(i)
     dd.barrier()
+    if args.profile_steps:  # a short untimed run for a profiler to attach to: nothing is measured or printed
+        for i in range(args.profile_steps):
+            rig.step(i)
+        torch.cuda.synchronize()
+        dd.close()
+        return
 
     # --- timed region: blocks of K steps, device-resident inputs --------------------------------
     with ClockSampler(local) as clocks:
@@ -811,6 +817,12 @@ def run_prefill(args):
     rig = PrefillRig(kvh, dev, rank)
     for _ in range(max(args.warmup, 3)):
         rig.step()
+    if args.profile_steps:
+        for _ in range(args.profile_steps):
+            rig.step()
+        torch.cuda.synchronize()
+        dd.close()
+        return
     with ClockSampler(local) as clocks:
         per_block, total_ms = time_blocks(rig.step, args.steps, args.min_seconds, dd)
     blocks = len(per_block)
@@ -875,6 +887,8 @@ def main():
     ap.add_argument("--parity", action="store_true", help="run the oracle check of the timed workload at one GPU too")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="run this many untimed steps after the warm-up and exit (for profiler captures)")
     ap.add_argument("--pool-blocks", type=int, default=0,
                     help="shrink the physical page pool (same sequences); for profiler captures only")
     args = ap.parse_args()

@@ -46,6 +46,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace nvllm {
 namespace prefill {
@@ -633,15 +634,19 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int q_pos = it.q0 + x * kTileQ + row;             // row of the sequence's query block
             const int first_lim = it.prefix + it.q0 + x * kTileQ;  // last key visible to the first row of this Q tile
             float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
-            for (int j = 0; ok && j < n_x; ++j, ++tiles) {
-                if (!(ok = wait_or_abort(sh, &sh->s_full[x], tiles & 1u))) break;
+            // One KV tile of this Q tile.  Tiles whose last key the tile's first row may still see need no mask; the
+            // one or two after them (one when the prefix is a multiple of the tile) are masked per element.  The two
+            // kinds run in two separate loops so that each loop body is straight-line code.
+            auto tile_step = [&](const int j, auto diag) -> bool {
+                constexpr bool kDiag = decltype(diag)::value;
+                if (!wait_or_abort(sh, &sh->s_full[x], tiles & 1u)) return false;
                 // A(j) starts after B(j-1); B(j) starts after A(j) while A still has tiles.
                 if (both && (x == 0 ? j >= 1 : j < it.n_a)) {
-                    if (!(ok = wait_or_abort(sh, &sh->turn[x ^ 1], turns_seen & 1u))) break;
+                    if (!wait_or_abort(sh, &sh->turn[x ^ 1], turns_seen & 1u)) return false;
                     ++turns_seen;
                 }
                 tc_fence_after();
-                if (it.ragged && j == it.n_kv - 1) {
+                if (kDiag && it.ragged && j == it.n_kv - 1) {
                     // The last KV tile of the sequence reaches past its last key: those rows of the V tile hold
                     // whatever follows in memory (the next sequence, padding, recycled cache rows).  Their
                     // probabilities are exactly zero, but 0 * NaN or 0 * Inf in the P.V product would still poison the
@@ -650,9 +655,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     // harmless: those scores are overwritten with -inf by the mask.  This warpgroup trails the MMA
                     // issuer, and the slot cannot be refilled before P.V of this very tile, so the parity wait sees
                     // either "still loading" or "landed", never another tile.  When both Q tiles use the tile both
-                    // warpgroups zero it (same bytes, same value).
+                    // warpgroups zero it (same bytes, same value).  (Such a tile is always a masked one.)
                     const uint32_t vpos = 2 * (kt0 + it.n_kv - 1) + 1;
-                    if (!(ok = wait_or_abort(sh, &sh->kv_full[vpos % kSlots], (vpos / kSlots) & 1u))) break;
+                    if (!wait_or_abort(sh, &sh->kv_full[vpos % kSlots], (vpos / kSlots) & 1u)) return false;
                     if (row >= it.len_k - (it.n_kv - 1) * kTileKV) {
                         // a row is 128 contiguous bytes in each 64-dim panel (the swizzle permutes inside a row)
                         uint8_t* vrow = sKV + (vpos % kSlots) * kTileBytes + row * 128;
@@ -664,19 +669,21 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         fence_proxy_async_smem();  // generic-proxy stores must be visible to the tensor core's reads
                     }
                 }
-                // the tile needs masking iff its last key lies beyond what the first row may see (one tile when the
-                // prefix is a multiple of the tile, two otherwise)
-                if (j * kTileKV + kTileKV - 1 > first_lim)
-                    ok = softmax_tile<true>(sh, x, t_s, t_o, first_lim - j * kTileKV + row, j == 0, (tiles - 1) & 1u,
-                                            p.scale_log2, m_run, m_used, l);
-                else
-                    ok = softmax_tile<false>(sh, x, t_s, t_o, 0, j == 0, (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l);
+                if (!softmax_tile<kDiag>(sh, x, t_s, t_o, kDiag ? first_lim - j * kTileKV + row : 0, j == 0,
+                                         (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l))
+                    return false;
                 // hand the turn over: A after each of its tiles, B while A still has a tile that will wait for it
                 if (both && (x == 0 || j + 1 < it.n_a)) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->turn[x]);
                 }
-            }
+                ++tiles;
+                return true;
+            };
+            const int n_plain = min(n_x, (first_lim + 1) / kTileKV);  // tiles j with j * 128 + 127 <= first_lim
+            int j = 0;
+            for (; ok && j < n_plain; ++j) ok = tile_step(j, std::false_type{});
+            for (; ok && j < n_x; ++j) ok = tile_step(j, std::true_type{});
             if (!ok) break;
             // ---- epilogue: O / l -> bf16 -> global, then hand O back to the MMA thread ----
             if (!(ok = wait_or_abort(sh, &sh->o_full[x], (tiles - 1) & 1u))) break;

@@ -23,12 +23,12 @@ def _alloc(lib, max_bytes):
 
 
 @pytest.mark.parametrize("world,count,with_residual", [(2, 8, False), (2, 128 * 4096, True), (4, 37 * 1024, False),
-                                                       (6, 128 * 4096, True), (3, 5000 * 8, True)])
+                                                       (4, 128 * 4096, True), (3, 5000 * 8, True)])
 def test_emulated_world_matches_the_host_sum_bit_for_bit(world, count, with_residual):
     import torch
     from nanovllm_jax_b200 import _lib
     lib = _lib.load()
-    max_bytes = 1 << 20  # (a world of 8 does not fit one device as co-resident blocks: it runs on 8 GPUs instead)
+    max_bytes = 1 << 20  # (worlds beyond 4 do not fit one device as co-resident blocks: they run on real GPUs instead)
     rng = np.random.Generator(np.random.PCG64(800 + world + count))
     xs = [_bf16_round(rng.standard_normal(count)) for _ in range(world)]
     res = [_bf16_round(rng.standard_normal(count)) for _ in range(world)] if with_residual else None
