@@ -7,9 +7,12 @@
 //
 //  * Work unit = one 64-token tile of one (sequence, kv head).  All tiles of
 //    one kv head are laid end to end (sequence after sequence) and cut into
-//    `num_groups` equal contiguous ranges ("stream-K" partition), so every CTA
-//    streams the same number of bytes no matter how skewed the context lengths
-//    are.  CTA c serves kv head c % KVH of group c / KVH; the KVH CTAs of a
+//    `num_groups` contiguous ranges of equal COST ("stream-K" partition): a tile
+//    costs one unit and every sequence kItemCost more in front of its tiles
+//    (the time a CTA loses at a sequence boundary -- q load, page lookup, the
+//    cross-warp combine -- measured at about four tile times).  So every CTA
+//    finishes at the same time no matter how skewed the context lengths are or
+//    how many short sequences fall into its range.  CTA c serves kv head c % KVH of group c / KVH; the KVH CTAs of a
 //    group walk the same tokens at the same pace, so the 256-byte per-head rows
 //    they fetch are neighbours in DRAM.
 //  * Persistent CTAs, 2 per SM: one producer warp issues TMA tile loads
@@ -50,6 +53,7 @@ constexpr int kWarps = kConsumerWarps + 1;     // consumers, TMA producer
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
+constexpr int kItemCost = 4;                   // cost of a sequence boundary in tile units (stream-K weights)
 constexpr int kPanelBytes = kTile * 128;       // 64 tokens x 64 dims bf16, 128B-swizzled
 constexpr int kTileBytes = 2 * kPanelBytes;    // one K or V tile
 constexpr int kQBytes = kMaxG * kD * 2;        // 2 KiB
@@ -99,31 +103,48 @@ __device__ __forceinline__ void mma_lo(float (&c)[4], uint32_t a0, uint32_t a2, 
         : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
 }
 
+// The cost line: sequence b with tb > 0 tiles occupies tb + kItemCost units, the first kItemCost of them standing
+// for its boundary overhead, the rest for its tiles 0 .. tb-1; empty sequences occupy nothing.
+__device__ __forceinline__ int units_of(int tb) { return tb > 0 ? tb + kItemCost : 0; }
+
 struct Walk {
-    int b, t;        // current sequence and tile within it
-    long long left;  // tiles still to serve in this CTA's range
+    int b;             // next sequence to look at
+    long long fv;      // unit at which sequence b starts
+    long long x0, x1;  // this CTA's range of units
+};
+struct Item {
+    int b, t0, n;      // sequence, first tile and number of tiles this CTA serves of it
+    int ctx, tb;       // its context length and total tiles
+    long long fv;      // unit at which the sequence starts (its tile 0 sits at fv + kItemCost)
 };
 
-// Advance to the next non-empty item; returns tiles in it (0 when done) and its context length.
-__device__ __forceinline__ int next_item(Walk& w, const Params& p, int max_ctx, int& ctx_out, int& tiles_out) {
-    while (w.left > 0 && w.b < p.B) {
-        const int ctx = clamp_ctx(__ldg(p.context_lens + w.b), max_ctx);
+// Advance to the next sequence of which this CTA serves at least one tile; false when the range is exhausted.
+// (hint_b, hint_ctx): a context length the caller has fetched ahead of time (hint_b < 0: none).
+__device__ __forceinline__ bool next_item(Walk& w, const Params& p, int max_ctx, Item& it, int hint_b = -1,
+                                          int hint_ctx = 0) {
+    while (w.b < p.B && w.fv < w.x1) {
+        const int ctx = clamp_ctx(w.b == hint_b ? hint_ctx : __ldg(p.context_lens + w.b), max_ctx);
         const int tb = tiles_of(ctx);
-        if (w.t >= tb) {
-            ++w.b;
-            w.t = 0;
-            continue;
-        }
-        long long n = tb - w.t;
-        if (n > w.left) n = w.left;
-        ctx_out = ctx;
-        tiles_out = tb;
-        return (int)n;
+        const long long t_base = w.fv + kItemCost;  // unit of tile 0
+        it.b = w.b;
+        it.fv = w.fv;
+        ++w.b;
+        w.fv += units_of(tb);
+        if (tb == 0) continue;
+        const long long lo = w.x0 - t_base, hi = w.x1 - t_base;
+        const int t0 = (int)(lo < 0 ? 0 : (lo > tb ? tb : lo));
+        const int t1 = (int)(hi < 0 ? 0 : (hi > tb ? tb : hi));
+        if (t0 >= t1) continue;  // only boundary units of this sequence fall into the range
+        it.t0 = t0;
+        it.n = t1 - t0;
+        it.ctx = ctx;
+        it.tb = tb;
+        return true;
     }
-    return 0;
+    return false;
 }
 
-// Combine the partials of sequence b (tiles [first, first + tb) of the per-head tile stream) for kv head kvh and
+// Combine the partials of sequence b (its tiles occupy units [first, first + tb) of the cost line) for kv head kvh and
 // write its G output rows.  Called by the 128 consumer threads: thread t owns row t / 16 and dims 8 (t % 16) ..
 // 8 (t % 16) + 7.  Partials are taken in group order, four at a time (all loads of a batch are independent), so the
 // result does not depend on which CTA runs this.
@@ -195,6 +216,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     uint64_t* empty_bar = full_bar + kStages;                          // [kStages]
     int* sm_i = reinterpret_cast<int*>(misc + 64);                     // scan scratch [8] + start [2] + abort [1]
     volatile int* sm_abort = sm_i + 12;
+    long long* sm_fv = reinterpret_cast<long long*>(sm_i + 14);       // unit at which the CTA's first sequence starts
     float* sm_ml = reinterpret_cast<float*>(misc + 128);               // [2 parities][m|l][4 warps][8 rows]
 
     const int tid = threadIdx.x;
@@ -226,7 +248,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     // page lookup read only settled memory and run ahead of the wait; the wait sits right before the first
     // access to anything the preparing kernel writes.
 
-    // ---- prologue: total tiles per head and the (sequence, tile) this CTA's range starts at ----
+    // ---- prologue: total cost units per head and the sequence this CTA's range starts in ----
     // Every CTA scans context_lens itself (B / 160 values per thread and one warp scan): that is one global
     // load latency, paid in parallel by all CTAs, and cheaper than fetching the result of a serial plan.
     const int per = (p.B + kThreads - 1) / kThreads;
@@ -234,7 +256,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     int mine = 0;
     for (int b = b_lo; b < b_hi; ++b) {
         const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
-        mine += tb;
+        mine += units_of(tb);
         if (tb == 0 && b % p.num_groups == group) {
             // an empty sequence attends to nothing: its rows are zeros (one CTA per kv head writes them)
             uint4* orow = reinterpret_cast<uint4*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G) * kD);
@@ -262,12 +284,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     {
         long long run = warp_off + incl - mine;
         for (int b = b_lo; b < b_hi; ++b) {
-            const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
-            if (tb > 0 && run <= x0 && x0 < run + tb) {
+            const int ub = units_of(tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx)));
+            if (ub > 0 && run <= x0 && x0 < run + ub) {
                 sm_i[10] = b;
-                sm_i[11] = (int)(x0 - run);
+                *sm_fv = run;
             }
-            run += tb;
+            run += ub;
         }
     }
     __syncthreads();
@@ -275,12 +297,17 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
 
     Walk walk;
     walk.b = sm_i[10];
-    walk.t = sm_i[11];
-    walk.left = x1 - x0;
+    walk.fv = *sm_fv;
+    walk.x0 = x0;
+    walk.x1 = x1;
     // page of the first tile, fetched ahead of the wait (block_tables is settled memory, see above)
     int first_phys = 0;
-    if (warp == kConsumerWarps && lane == 0)
-        first_phys = __ldg(p.block_tables + (size_t)walk.b * p.MB + (walk.t * kTile) / p.block_size);
+    if (warp == kConsumerWarps && lane == 0) {
+        Walk peek = walk;
+        Item first;
+        if (next_item(peek, p, max_ctx, first))
+            first_phys = __ldg(p.block_tables + (size_t)first.b * p.MB + (first.t0 * kTile) / p.block_size);
+    }
     griddep_wait();
 
     if (warp == kConsumerWarps) {
@@ -288,20 +315,24 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             uint32_t it = 0;
-            int ctx, tb, n;
+            Item item;
             bool ok = true;
-            while (ok && (n = next_item(walk, p, max_ctx, ctx, tb)) > 0) {
-                const int32_t* bt = p.block_tables + (size_t)walk.b * p.MB;
-                for (int i = 0; i < n; ++i, ++it) {
+            // Metadata of the sequence after the current one is fetched one item ahead (its length and its first
+            // page: every item but a CTA's first starts at tile 0), so that a sequence boundary does not put two
+            // dependent global-load latencies between two tile requests.
+            int pf_b = -1, pf_ctx = 0, pf_phys = 0;
+            while (ok && next_item(walk, p, max_ctx, item, pf_b, pf_ctx)) {
+                const int32_t* bt = p.block_tables + (size_t)item.b * p.MB;
+                for (int i = 0; i < item.n; ++i, ++it) {
                     const int stage = it % kStages;
                     const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
                     if (*sm_abort || !mbar_wait(empty_bar + stage, parity)) {
                         ok = false;
                         break;
                     }
-                    const int tok0 = (walk.t + i) * kTile;
+                    const int tok0 = (item.t0 + i) * kTile;
                     const int bi = tok0 / p.block_size;
-                    int phys = it == 0 ? first_phys : __ldg(bt + bi);
+                    int phys = it == 0 ? first_phys : ((i == 0 && item.b == pf_b && bi == 0) ? pf_phys : __ldg(bt + bi));
                     phys = phys < 0 ? 0 : (phys >= p.NB ? p.NB - 1 : phys);
                     const int slot = phys * p.block_size + (tok0 - bi * p.block_size);
                     uint8_t* st = smem + stage * kStageBytes;
@@ -312,12 +343,16 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     tma_load_3d_hint(st + kPanelBytes, &tm_k, bar, 64, kvh, slot, pol);
                     tma_load_3d_hint(st + kTileBytes, &tm_v, bar, 0, kvh, slot, pol);
                     tma_load_3d_hint(st + kTileBytes + kPanelBytes, &tm_v, bar, 64, kvh, slot, pol);
-                    if (i == 0)
-                        bulk_load(st + 2 * kTileBytes, p.q + ((size_t)walk.b * p.H + (size_t)kvh * p.G) * kD, qbytes,
+                    if (i == 0) {
+                        bulk_load(st + 2 * kTileBytes, p.q + ((size_t)item.b * p.H + (size_t)kvh * p.G) * kD, qbytes,
                                   bar);
+                        if (walk.b < p.B) {  // the loads are issued now and first used at the next boundary
+                            pf_b = walk.b;
+                            pf_ctx = __ldg(p.context_lens + walk.b);
+                            pf_phys = __ldg(p.block_tables + (size_t)walk.b * p.MB);
+                        }
+                    }
                 }
-                walk.left -= n;
-                walk.t += n;
             }
             if (!ok) {
                 *sm_abort = 1;
@@ -338,11 +373,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int tok_base = warp * 16;
     const int ctid = tid;            // 0..127 among consumers
     uint32_t it = 0, item = 0;
-    int ctx, tb, n;
+    Item cur;
     bool ok = true;
 
-    for (; ok && (n = next_item(walk, p, max_ctx, ctx, tb)) > 0; ++item) {
-        const bool full_item = (walk.t == 0 && walk.t + n == tb);
+    for (; ok && next_item(walk, p, max_ctx, cur); ++item) {
+        const int n = cur.n, ctx = cur.ctx, tb = cur.tb;
+        const bool full_item = (cur.t0 == 0 && n == tb);
         // (m, l) exchange buffers alternate between consecutive items so that a warp that races ahead
         // into the next item cannot overwrite values a slower warp is still reading.
         float* sm_m = sm_ml + (item & 1u) * (2 * kConsumerWarps * kMaxG);
@@ -368,7 +404,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     qa[ks][1] = row < p.G ? qs[row * 64 + ks * 8 + 4 + quad] : 0u;
                 }
             }
-            const int valid = ctx - ((walk.t + i) * kTile + tok_base);  // live tokens in this warp's 16-token slice
+            const int valid = ctx - ((cur.t0 + i) * kTile + tok_base);  // live tokens in this warp's 16-token slice
             if (valid > 0) {
                 const uint32_t kbase = smem_u32(st);
                 const uint32_t vbase = kbase + kTileBytes;
@@ -477,7 +513,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         {
             float* part = nullptr;
             if (!full_item)
-                part = p.partials + ((size_t)blockIdx.x * 2 + (walk.t == 0 ? 1 : 0)) * partial_floats(p.G);
+                part = p.partials + ((size_t)blockIdx.x * 2 + (cur.t0 == 0 ? 1 : 0)) * partial_floats(p.G);
             for (int r = 0; r < p.G; ++r) {
                 float mt = -INFINITY;
 #pragma unroll
@@ -490,7 +526,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 }
                 const float acc = Os[r * kOsStride + ctid] + Os[(kMaxG + r) * kOsStride + ctid];
                 if (full_item) {
-                    p.out[((size_t)walk.b * p.H + (size_t)kvh * p.G + r) * kD + ctid] =
+                    p.out[((size_t)cur.b * p.H + (size_t)kvh * p.G + r) * kD + ctid] =
                         __float2bfloat16_rn(acc / (lt + 1e-9f));
                 } else {
                     part[r * kD + ctid] = acc;
@@ -505,20 +541,18 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 // ticket finds every partial of the sequence visible and combines them; nobody waits.
                 __threadfence();
                 named_barrier_sync(1, kConsumerWarps * 32);
-                if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)walk.b * p.KVH + kvh, 1u);
+                if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)cur.b * p.KVH + kvh, 1u);
                 named_barrier_sync(1, kConsumerWarps * 32);
-                const long long first = (x1 - walk.left) - walk.t;  // index of the sequence's tile 0 in the stream
-                long long parts = tb;  // fewer tiles than groups: every non-empty group holds exactly one tile
+                const long long first = cur.fv + kItemCost;  // unit of the sequence's tile 0 on the cost line
+                long long parts = tb;  // fewer units than groups: every non-empty group holds exactly one unit
                 if (total >= p.num_groups)
                     parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
                 if ((long long)sm_i[9] == parts - 1) {
                     __threadfence();
-                    merge_sequence(p, walk.b, kvh, first, tb, total, ctid);
+                    merge_sequence(p, cur.b, kvh, first, tb, total, ctid);
                 }
             }
         }
-        walk.left -= n;
-        walk.t += n;
     }
     if (!ok) {
         *sm_abort = 1;

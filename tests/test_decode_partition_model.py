@@ -7,41 +7,49 @@ import numpy as np
 from hypothesis import given, settings, strategies as st
 
 TILE = 64
+ITEM_COST = 4  # kItemCost: units a sequence boundary costs in front of the sequence's tiles
 
 
 def tiles_of(ctx):
     return (ctx + TILE - 1) // TILE
 
 
+def units_of(tb):
+    return tb + ITEM_COST if tb > 0 else 0
+
+
 def main_kernel_model(ctx, num_groups):
-    """Returns (direct, partial): direct = set of sequences written straight to `out`; partial[(group, slot)] = (b, t0, t1)."""
+    """Returns (direct, partial, served, first_unit, total): direct = set of sequences written straight to `out`;
+    partial[(group, slot)] = (b, t0, t1); first_unit[b] = unit of b's tile 0 on the cost line."""
     tiles = [tiles_of(c) for c in ctx]
-    total = sum(tiles)
-    prefix = np.concatenate([[0], np.cumsum(tiles)])
-    direct, partial, served = set(), {}, np.zeros(max(total, 1), dtype=np.int32)
+    units = [units_of(t) for t in tiles]
+    total = sum(units)
+    start = np.concatenate([[0], np.cumsum(units)])
+    first_unit = [int(start[b]) + ITEM_COST for b in range(len(ctx))]
+    direct, partial = set(), {}
+    served = [np.zeros(t, dtype=np.int32) for t in tiles]
     for g in range(num_groups):
         x0, x1 = g * total // num_groups, (g + 1) * total // num_groups
         if x0 >= x1:
             continue
-        # the (b, t) containing global tile x0: the sequence with tiles > 0 and prefix <= x0 < prefix + tiles
-        b = next(i for i in range(len(ctx)) if tiles[i] > 0 and prefix[i] <= x0 < prefix[i] + tiles[i])
-        t, left = x0 - prefix[b], x1 - x0
-        while left > 0:
-            if t >= tiles[b]:
-                b, t = b + 1, 0
-                continue
-            n = min(tiles[b] - t, left)
-            served[prefix[b] + t: prefix[b] + t + n] += 1
-            if t == 0 and t + n == tiles[b]:
-                assert b not in direct
-                direct.add(b)
-            else:
-                slot = 1 if t == 0 else 0
-                assert (g, slot) not in partial, "a CTA would overwrite one of its two partial slots"
-                partial[(g, slot)] = (b, t, t + n)
-            left -= n
-            t += n
-    return direct, partial, served[:total], prefix, total
+        # the walk of the kernel: start at the sequence whose units contain x0, go on while sequences start before x1
+        b = next(i for i in range(len(ctx)) if units[i] > 0 and start[i] <= x0 < start[i] + units[i])
+        while b < len(ctx) and start[b] < x1:
+            tb = tiles[b]
+            if tb > 0:
+                t0 = min(max(x0 - first_unit[b], 0), tb)
+                t1 = min(max(x1 - first_unit[b], 0), tb)
+                if t0 < t1:
+                    served[b][t0:t1] += 1
+                    if t0 == 0 and t1 == tb:
+                        assert b not in direct
+                        direct.add(b)
+                    else:
+                        slot = 1 if t0 == 0 else 0
+                        assert (g, slot) not in partial, "a CTA would overwrite one of its two partial slots"
+                        partial[(g, slot)] = (b, t0, t1)
+            b += 1
+    return direct, partial, served, first_unit, total
 
 
 def expected_tickets(first, tb, total, num_groups):
@@ -51,11 +59,8 @@ def expected_tickets(first, tb, total, num_groups):
     return tb
 
 
-def merge_kernel_model(b, prefix, total, num_groups):
-    """Slots merge_sequence reads for sequence b ('zero' if the row is zero-filled, None if nothing is combined)."""
-    first, tb = int(prefix[b]), int(prefix[b + 1] - prefix[b])
-    if tb == 0:
-        return "zero"
+def merge_model(first, tb, total, num_groups):
+    """Slots merge_sequence reads for a sequence whose tiles occupy units [first, first + tb) (None: nothing to combine)."""
     gf = min(((first + 1) * num_groups - 1) // total, num_groups - 1)
     gl = min(((first + tb) * num_groups - 1) // total, num_groups - 1)
     if gf == gl:
@@ -72,33 +77,44 @@ def merge_kernel_model(b, prefix, total, num_groups):
 @given(st.lists(st.integers(min_value=0, max_value=3000), min_size=1, max_size=40),
        st.sampled_from([1, 2, 3, 5, 18, 37, 74, 148, 296]))
 def test_every_tile_once_and_merge_reads_what_was_written(ctx, num_groups):
-    direct, partial, served, prefix, total = main_kernel_model(ctx, num_groups)
-    assert np.all(served == 1), "each tile of each sequence is streamed by exactly one CTA"
+    direct, partial, served, first_unit, total = main_kernel_model(ctx, num_groups)
+    for b, sv in enumerate(served):
+        assert np.all(sv == 1), "each tile of each sequence is streamed by exactly one CTA"
     by_seq = {}
     for (g, slot), (b, t0, t1) in partial.items():
         by_seq.setdefault(b, []).append((g, slot, t0, t1))
     for b, c in enumerate(ctx):
-        want = merge_kernel_model(b, prefix, total, num_groups) if total > 0 else "zero"
-        if tiles_of(c) == 0:
-            assert want == "zero" and b not in direct and b not in by_seq
-        elif b in direct:
+        tb = tiles_of(c)
+        if tb == 0:
+            assert b not in direct and b not in by_seq  # zero-filled in the prologue
+            continue
+        want = merge_model(first_unit[b], tb, total, num_groups)
+        if b in direct:
             assert want is None and b not in by_seq, "a directly written row must not be merged again"
         else:
             pieces = sorted(by_seq[b])
-            assert want is not None and want != "zero"
+            assert want is not None
             assert sorted(want) == [(g, s) for g, s, _, _ in pieces], (ctx, num_groups, b, want, pieces)
-            assert expected_tickets(int(prefix[b]), tiles_of(c), total, num_groups) == len(pieces)
+            assert expected_tickets(first_unit[b], tb, total, num_groups) == len(pieces)
             # the pieces tile the sequence without gap or overlap
             spans = sorted((t0, t1) for _, _, t0, t1 in pieces)
-            assert spans[0][0] == 0 and spans[-1][1] == tiles_of(c)
+            assert spans[0][0] == 0 and spans[-1][1] == tb
             assert all(a[1] == n[0] for a, n in zip(spans, spans[1:]))
 
 
+def test_cost_weights_even_out_ranges_with_many_short_sequences():
+    """64 one-tile sequences followed by one of 640 tiles, two groups: by tiles alone the first group would take all the
+    short sequences plus 288 tiles; with the boundary cost it takes them plus 160 tiles only."""
+    direct, partial, served, first_unit, total = main_kernel_model([10] * 64 + [640 * 64], 2)
+    assert total == 64 * 5 + 644
+    assert partial[(0, 1)] == (64, 0, 158) and partial[(1, 0)] == (64, 158, 640)
+
+
 def test_known_shapes():
-    # one tile, 37 groups: only the last group works, nothing to merge
-    direct, partial, served, prefix, total = main_kernel_model([1], 37)
+    # one tile, 37 groups: one group works, nothing to merge
+    direct, partial, served, first_unit, total = main_kernel_model([1], 37)
     assert direct == {0} and not partial
-    # one long sequence over 37 groups: 37 pieces, slot 1 in the first group, slot 0 elsewhere
-    direct, partial, _, prefix, total = main_kernel_model([32768], 37)
+    # one long sequence over 37 groups: every group but those holding only boundary units serves a piece
+    direct, partial, _, first_unit, total = main_kernel_model([32768], 37)
     assert not direct and len(partial) == 37
-    assert merge_kernel_model(0, prefix, total, 37) == [(0, 1)] + [(g, 0) for g in range(1, 37)]
+    assert merge_model(first_unit[0], 512, total, 37) == [(0, 1)] + [(g, 0) for g in range(1, 37)]
