@@ -8,9 +8,9 @@
 //  * Work unit = one 64-token tile of one (sequence, kv head).  All tiles of
 //    one kv head are laid end to end (sequence after sequence) and cut into
 //    `num_groups` contiguous ranges of equal COST ("stream-K" partition): a tile
-//    costs one unit and every sequence kItemCost more in front of its tiles
-//    (the time a CTA loses at a sequence boundary -- q load, page lookup, the
-//    cross-warp combine -- measured at about four tile times).  So every CTA
+//    costs one unit and every sequence two more in front of its tiles (the
+//    time a CTA loses at a sequence boundary -- q load, page lookup, the
+//    cross-warp combine -- measured at one to two tile times).  So every CTA
 //    finishes at the same time no matter how skewed the context lengths are or
 //    how many short sequences fall into its range.  CTA c serves kv head c % KVH of group c / KVH; the KVH CTAs of a
 //    group walk the same tokens at the same pace, so the 256-byte per-head rows
@@ -41,6 +41,7 @@
 #include "store_kvcache.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 #include <string.h>
 
 namespace nvllm {
@@ -53,7 +54,7 @@ constexpr int kWarps = kConsumerWarps + 1;     // consumers, TMA producer
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
-constexpr int kItemCost = 4;                   // cost of a sequence boundary in tile units (stream-K weights)
+constexpr int kItemCostDefault = 2;            // cost of a sequence boundary in tile units (stream-K weights)
 constexpr int kPanelBytes = kTile * 128;       // 64 tokens x 64 dims bf16, 128B-swizzled
 constexpr int kTileBytes = 2 * kPanelBytes;    // one K or V tile
 constexpr int kQBytes = kMaxG * kD * 2;        // 2 KiB
@@ -78,6 +79,7 @@ struct Params {
     unsigned int* tickets;  // [B*KVH] partials delivered so far per (sequence, kv head); zero when the kernel starts
     int B, H, KVH, G, NB, block_size, MB;
     int num_groups;
+    int item_cost;  // units a sequence boundary costs on the cost line (see units_of)
     float scale_log2;
 };
 
@@ -103,9 +105,9 @@ __device__ __forceinline__ void mma_lo(float (&c)[4], uint32_t a0, uint32_t a2, 
         : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
 }
 
-// The cost line: sequence b with tb > 0 tiles occupies tb + kItemCost units, the first kItemCost of them standing
+// The cost line: sequence b with tb > 0 tiles occupies tb + item_cost units, the first item_cost of them standing
 // for its boundary overhead, the rest for its tiles 0 .. tb-1; empty sequences occupy nothing.
-__device__ __forceinline__ int units_of(int tb) { return tb > 0 ? tb + kItemCost : 0; }
+__device__ __forceinline__ int units_of(int tb, int item_cost) { return tb > 0 ? tb + item_cost : 0; }
 
 struct Walk {
     int b;             // next sequence to look at
@@ -115,7 +117,7 @@ struct Walk {
 struct Item {
     int b, t0, n;      // sequence, first tile and number of tiles this CTA serves of it
     int ctx, tb;       // its context length and total tiles
-    long long fv;      // unit at which the sequence starts (its tile 0 sits at fv + kItemCost)
+    long long fv;      // unit at which the sequence starts (its tile 0 sits at fv + item_cost)
 };
 
 // Advance to the next sequence of which this CTA serves at least one tile; false when the range is exhausted.
@@ -125,11 +127,11 @@ __device__ __forceinline__ bool next_item(Walk& w, const Params& p, int max_ctx,
     while (w.b < p.B && w.fv < w.x1) {
         const int ctx = clamp_ctx(w.b == hint_b ? hint_ctx : __ldg(p.context_lens + w.b), max_ctx);
         const int tb = tiles_of(ctx);
-        const long long t_base = w.fv + kItemCost;  // unit of tile 0
+        const long long t_base = w.fv + p.item_cost;  // unit of tile 0
         it.b = w.b;
         it.fv = w.fv;
         ++w.b;
-        w.fv += units_of(tb);
+        w.fv += units_of(tb, p.item_cost);
         if (tb == 0) continue;
         const long long lo = w.x0 - t_base, hi = w.x1 - t_base;
         const int t0 = (int)(lo < 0 ? 0 : (lo > tb ? tb : lo));
@@ -256,7 +258,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     int mine = 0;
     for (int b = b_lo; b < b_hi; ++b) {
         const int tb = tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx));
-        mine += units_of(tb);
+        mine += units_of(tb, p.item_cost);
         if (tb == 0 && b % p.num_groups == group) {
             // an empty sequence attends to nothing: its rows are zeros (one CTA per kv head writes them)
             uint4* orow = reinterpret_cast<uint4*>(p.out + ((size_t)b * p.H + (size_t)kvh * p.G) * kD);
@@ -284,7 +286,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     {
         long long run = warp_off + incl - mine;
         for (int b = b_lo; b < b_hi; ++b) {
-            const int ub = units_of(tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx)));
+            const int ub = units_of(tiles_of(clamp_ctx(__ldg(p.context_lens + b), max_ctx)), p.item_cost);
             if (ub > 0 && run <= x0 && x0 < run + ub) {
                 sm_i[10] = b;
                 *sm_fv = run;
@@ -543,7 +545,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 named_barrier_sync(1, kConsumerWarps * 32);
                 if (ctid == 0) sm_i[9] = (int)atomicAdd(p.tickets + (size_t)cur.b * p.KVH + kvh, 1u);
                 named_barrier_sync(1, kConsumerWarps * 32);
-                const long long first = cur.fv + kItemCost;  // unit of the sequence's tile 0 on the cost line
+                const long long first = cur.fv + p.item_cost;  // unit of the sequence's tile 0 on the cost line
                 long long parts = tb;  // fewer units than groups: every non-empty group holds exactly one unit
                 if (total >= p.num_groups)
                     parts = ((first + tb) * p.num_groups - 1) / total - ((first + 1) * p.num_groups - 1) / total + 1;
@@ -597,6 +599,16 @@ decode_prepare_fused_kernel(unsigned int* __restrict__ tickets, int num_tickets,
 // host side
 // ---------------------------------------------------------------------------
 static int main_grid() { return kCtasPerSm * sm_count(); }
+
+// NVLLM_B200_ITEM_COST overrides the boundary weight of the stream-K partition (an experiment knob; 0 = by tiles only).
+static int item_cost() {
+    static const int v = [] {
+        const char* e = getenv("NVLLM_B200_ITEM_COST");
+        const int x = e ? atoi(e) : kItemCostDefault;
+        return x < 0 ? 0 : (x > 64 ? 64 : x);
+    }();
+    return v;
+}
 
 static size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 
@@ -728,6 +740,7 @@ static int launch_decode(const char* who, const DecodeArgs& a, const StepArgs* s
     p.block_size = a.block_size;
     p.MB = a.MB;
     p.num_groups = main_grid() / a.KVH;
+    p.item_cost = item_cost();
     p.scale_log2 = a.scale * 1.4426950408889634f;
 
     cudaLaunchAttribute attr[1];
