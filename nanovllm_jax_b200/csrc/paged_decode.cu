@@ -8,9 +8,9 @@
 //  * Work unit = one 64-token tile of one (sequence, kv head).  All tiles of
 //    one kv head are laid end to end (sequence after sequence) and cut into
 //    `num_groups` contiguous ranges of equal COST ("stream-K" partition): a tile
-//    costs one unit and every sequence two more in front of its tiles (the
+//    costs one unit and every sequence four more in front of its tiles (the
 //    time a CTA loses at a sequence boundary -- q load, page lookup, the
-//    cross-warp combine -- measured at one to two tile times).  So every CTA
+//    cross-warp combine, and the partial results at the ends of a range).  So every CTA
 //    finishes at the same time no matter how skewed the context lengths are or
 //    how many short sequences fall into its range.  CTA c serves kv head c % KVH of group c / KVH; the KVH CTAs of a
 //    group walk the same tokens at the same pace, so the 256-byte per-head rows
@@ -54,7 +54,7 @@ constexpr int kWarps = kConsumerWarps + 1;     // consumers, TMA producer
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kMaxG = 8;                       // query heads per kv head packed in one CTA
-constexpr int kItemCostDefault = 2;            // cost of a sequence boundary in tile units (stream-K weights)
+constexpr int kItemCostDefault = 4;            // cost of a sequence boundary in tile units (stream-K weights)
 constexpr int kPanelBytes = kTile * 128;       // 64 tokens x 64 dims bf16, 128B-swizzled
 constexpr int kTileBytes = 2 * kPanelBytes;    // one K or V tile
 constexpr int kQBytes = kMaxG * kD * 2;        // 2 KiB

@@ -7,7 +7,7 @@ import numpy as np
 from hypothesis import given, settings, strategies as st
 
 TILE = 64
-ITEM_COST = 2  # kItemCostDefault: units a sequence boundary costs in front of the sequence's tiles
+ITEM_COST = 4  # kItemCostDefault: units a sequence boundary costs in front of the sequence's tiles
 
 
 def tiles_of(ctx):
@@ -104,10 +104,10 @@ def test_every_tile_once_and_merge_reads_what_was_written(ctx, num_groups):
 
 def test_cost_weights_even_out_ranges_with_many_short_sequences():
     """64 one-tile sequences followed by one of 640 tiles, two groups: by tiles alone the first group would take all the
-    short sequences plus 288 tiles; with the boundary cost it takes them plus 223 tiles only."""
+    short sequences plus 288 tiles; with the boundary cost it takes them plus 158 tiles only."""
     direct, partial, served, first_unit, total = main_kernel_model([10] * 64 + [640 * 64], 2)
-    assert total == 64 * 3 + 642
-    assert partial[(0, 1)] == (64, 0, 223) and partial[(1, 0)] == (64, 223, 640)
+    assert total == 64 * 5 + 644
+    assert partial[(0, 1)] == (64, 0, 158) and partial[(1, 0)] == (64, 158, 640)
 
 
 def test_known_shapes():
