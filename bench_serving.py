@@ -23,8 +23,10 @@ Pages are dealt the way the reference's block manager deals them (engine/block_m
 in order, a new block when a sequence crosses a block boundary); ``tests/test_serving_tables.py`` holds this to
 tables produced by the reference's own code.
 
-With one rank the decode step is replayed from a CUDA graph; with more than one rank it is launched eagerly (a graph
-that contains collectives of several ranks is not attempted).  The model is NOT part of the library; it exists so that
+The decode step is replayed from a CUDA graph.  With more than one rank that holds only when the reductions are this
+library's kernels (``--allreduce peer``: ordinary kernels that number their calls on the device, so a replay is a new
+call; their waits are bounded, so a rank that falls out of step ends in a status bit, not a hang); with
+``--allreduce nccl`` the step is launched eagerly -- NCCL collectives of several ranks are not captured.  The model is NOT part of the library; it exists so that
 the attention path can be timed inside a realistic decode step.  Weights are N(0, 0.02) random (there is no checkpoint
 in the image), drawn per head group so that the full model is the same at every tensor-parallel size; prompts are
 uniform random token ids.  Prints one JSON line on rank 0.
@@ -279,7 +281,8 @@ class Engine:
             torch.cuda.synchronize()
             try:
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                # thread_local: another thread of the process (NCCL's watchdog) may touch CUDA during the capture
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     self._decode_step_device()
                 self.graph = g
             except Exception as exc:  # capture unsupported here: run the step eagerly and say so
@@ -339,7 +342,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--layers", type=int, default=36)
-    ap.add_argument("--no-graph", action="store_true", help="one rank: launch the decode step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--allreduce", choices=["peer", "nccl"], default="peer")
     ap.add_argument("--unfused", action="store_true", help="torch q_norm / k_norm / RoPE and separate store instead of the fused kernels")
     args = ap.parse_args()
@@ -377,7 +380,7 @@ def main():
     torch.cuda.synchronize()
     t_prefill = time.perf_counter() - t0
     _stage(f"prefill done in {t_prefill:.2f}s")
-    use_graph = (not args.no_graph) and world == 1
+    use_graph = (not args.no_graph) and (world == 1 or reducer is not None)
     model.allreduce_calls = 0
     tokens, t_decode = eng.decode(first, use_graph=use_graph)
     _stage(f"decode done in {t_decode:.2f}s")

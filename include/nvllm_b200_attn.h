@@ -289,7 +289,11 @@ int nvllm_b200_fused_decode_step(void* q, void* k, const void* v, const float* q
  *   comm_open    maps a peer's buffer from its handle; comm_close unmaps it; comm_free frees one's own.
  * allreduce_sum: out = sum over ranks of in (+ residual), `count` bf16 elements (a multiple of 8, count*2 <= max_bytes).
  *   buffers_host  HOST array of `world` device pointers: entry r = rank r's buffer as mapped in this process
- *   epoch         1, 2, 3, ... : the same value on every rank for the same call, increasing by one per call
+ *   epoch         0: the kernel numbers the calls itself (a counter in the rank's buffer, advanced by every call;
+ *                 all ranks count alike because they issue the same calls) -- the mode to use under CUDA-graph
+ *                 capture, where kernel parameters are frozen; or 1, 2, 3, ...: the caller numbers the calls, the
+ *                 same value on every rank for the same call, increasing by one per call.  One communicator uses
+ *                 one mode throughout
  *   max_spins     bound of the wait for the peers' flags; when it runs out the call's kernel raises bit 6 (64) of
  *                 nvllm_b200_device_status, leaves `out` unwritten for the affected parts and returns
  * in, out and residual may alias one another.  Results are bit-identical on every rank (fixed summation order).

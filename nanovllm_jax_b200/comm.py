@@ -65,11 +65,11 @@ class PeerAllReduce:
             return x
         if residual is not None and (residual.dtype != x.dtype or residual.shape != x.shape or not residual.is_contiguous()):
             raise ValueError("residual must match x")
-        self.epoch = (self.epoch + 1) & 0xFFFFFFFF  # compared modulo 2^32 on the device
+        self.epoch += 1  # bookkeeping only: the kernel numbers the calls itself (epoch 0), which survives graph replay
         with torch.cuda.device(self.device):
             _lib.check(self._lib.nvllm_b200_allreduce_sum(
                 x.data_ptr(), x.data_ptr(), residual.data_ptr() if residual is not None else None, self._ptrs,
-                self.rank, self.world, x.numel(), self.max_bytes, self.epoch, self.max_spins,
+                self.rank, self.world, x.numel(), self.max_bytes, 0, self.max_spins,
                 torch.cuda.current_stream(self.device).cuda_stream))
         return x
 

@@ -6,7 +6,10 @@
 // Optionally adds the residual stream in the same pass (x = x + sum, models/qwen3.py:225-231).
 //
 // Every rank owns one "symmetric" buffer (same layout on every rank, mapped into every other rank's address space
-// through CUDA IPC):  flags[world][kCtas] u32, then two staging slots of max_bytes each.  One call with epoch e:
+// through CUDA IPC):  flags[world][kCtas] u32, a control block (calls completed, CTAs finished), then two staging
+// slots of max_bytes each.  One call with epoch e (given by the caller, or -- epoch 0 -- taken from the control
+// block as "calls completed + 1", which every rank counts alike; only the latter survives CUDA-graph replay, where
+// kernel parameters are frozen):
 //   1. CTA c copies its chunks of the input into the rank's own staging slot e & 1;
 //   2. it publishes them: system-scope fence, then flags[rank][c] = e written into EVERY peer's buffer;
 //   3. it waits until its own flags[p][c] >= e for every peer p (a bounded spin on LOCAL memory);
@@ -32,7 +35,8 @@ constexpr int kMaxWorld = 8;
 
 __device__ int g_error_flag = 0;  // bit 6 (64): a peer's flag did not arrive in time
 
-__host__ __device__ inline size_t flag_bytes() { return (size_t)kMaxWorld * kCtas * 4; }
+__host__ __device__ inline size_t flag_bytes() { return (size_t)kMaxWorld * kCtas * 4 + 256; }  // flags + control block
+__host__ __device__ inline size_t ctrl_offset() { return (size_t)kMaxWorld * kCtas * 4; }
 
 struct Params {
     // one entry per emulated rank (blockIdx.y); a real multi-GPU launch uses entry 0 only
@@ -45,7 +49,7 @@ struct Params {
     long long chunks;                     // ceil(bytes / kChunkBytes)
     long long vecs;                       // bytes / 16
     size_t max_bytes;
-    unsigned int epoch;
+    unsigned int epoch;  // 0: use the device-side call counter of the rank's control block
     long long max_spins;
 };
 
@@ -75,9 +79,12 @@ __global__ void __launch_bounds__(kThreads) allreduce_sum_kernel(const Params p)
     __shared__ int s_ok;
     const int y = blockIdx.y, rank = p.rank0 + y, c = blockIdx.x, tid = threadIdx.x;
     uint8_t* mine = p.bufs[y][rank];
-    const size_t slot_off = flag_bytes() + (size_t)(p.epoch & 1u) * p.max_bytes;
-    griddep_wait();  // the input comes from the kernel just before this one (the row-parallel GEMM)
+    unsigned int* ctrl = reinterpret_cast<unsigned int*>(mine + ctrl_offset());  // [0] calls completed, [1] CTAs finished
+    griddep_wait();  // the input comes from the kernel just before this one (the row-parallel GEMM); so does ctrl[0]
     griddep_launch_dependents();
+    // every CTA of the launch reads the same value: ctrl[0] only moves when the last CTA of a launch has finished
+    const unsigned int epoch = p.epoch ? p.epoch : *reinterpret_cast<volatile unsigned int*>(ctrl) + 1u;
+    const size_t slot_off = flag_bytes() + (size_t)(epoch & 1u) * p.max_bytes;
     if (tid == 0) s_ok = 1;
     // 1. my chunks -> my staging slot
     uint4* stage = reinterpret_cast<uint4*>(mine + slot_off);
@@ -89,13 +96,13 @@ __global__ void __launch_bounds__(kThreads) allreduce_sum_kernel(const Params p)
     __syncthreads();
     if (tid < p.world && tid != rank) {
         __threadfence_system();
-        st_flag_sys(reinterpret_cast<unsigned int*>(p.bufs[y][tid]) + rank * kCtas + c, p.epoch);
+        st_flag_sys(reinterpret_cast<unsigned int*>(p.bufs[y][tid]) + rank * kCtas + c, epoch);
     }
     // 3. wait for every peer's CTA c (bounded; the flags I poll live in my own memory)
     if (tid < p.world && tid != rank) {
         const unsigned int* f = reinterpret_cast<const unsigned int*>(mine) + tid * kCtas + c;
         long long spins = 0;
-        while ((int)(ld_flag_sys(f) - p.epoch) < 0) {
+        while ((int)(ld_flag_sys(f) - epoch) < 0) {
             if (++spins > p.max_spins) {
                 s_ok = 0;
                 atomicOr(&g_error_flag, 64);
@@ -104,9 +111,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_sum_kernel(const Params p)
         }
     }
     __syncthreads();
-    if (!s_ok) return;
-    // 4. sum in rank order
-    for (long long ch = c; ch < p.chunks; ch += kCtas) {
+    // 4. sum in rank order (skipped when a peer never delivered)
+    for (long long ch = c; s_ok && ch < p.chunks; ch += kCtas) {
         const long long i = ch * kThreads + tid;
         if (i >= p.vecs) continue;
         uint4 v[kMaxWorld];
@@ -126,6 +132,15 @@ __global__ void __launch_bounds__(kThreads) allreduce_sum_kernel(const Params p)
         w.z = pack_bf16(acc[4], acc[5]);
         w.w = pack_bf16(acc[6], acc[7]);
         p.out[y][i] = w;
+    }
+    // 5. the last CTA of this rank's launch to get here advances the rank's call counter
+    __syncthreads();
+    if (tid == 0) {
+        if (atomicAdd(ctrl + 1, 1u) == (unsigned int)kCtas - 1u) {
+            ctrl[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(ctrl) = epoch;
+        }
     }
 }
 

@@ -56,6 +56,29 @@ def test_emulated_world_matches_the_host_sum_bit_for_bit(world, count, with_resi
     assert _lib.device_status() == 0
 
 
+def test_calls_numbered_on_the_device():
+    """epoch 0: the kernel takes the call number from the counter in each rank's buffer, so the very same launch
+    parameters (what a CUDA-graph replay re-issues) make a new call every time."""
+    import torch
+    from nanovllm_jax_b200 import _lib
+    lib = _lib.load()
+    world, count, max_bytes = 3, 6 * 4096, 1 << 18
+    bufs = [_alloc(lib, max_bytes) for _ in range(world)]
+    ins = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(count, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    arr = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+    a_in, a_out, a_buf = arr(ins), arr(outs), arr(bufs)
+    for call in range(1, 6):
+        for r, t in enumerate(ins):
+            t.fill_(float(call * (r + 1)))
+        _lib.check(lib.nvllm_b200_allreduce_sum_emulated(a_in, a_out, None, a_buf, world, count, max_bytes, 0, 1 << 22,
+                                                         torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        for o in outs:
+            assert bool((o == float(6 * call)).all()), call
+    assert _lib.device_status() == 0
+
+
 def test_in_place_and_size_limits():
     import torch
     from nanovllm_jax_b200 import _lib
