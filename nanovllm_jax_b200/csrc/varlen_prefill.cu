@@ -349,7 +349,8 @@ __device__ __forceinline__ int kv_tile_token(const Params& p, const Item& it, in
 template <bool DIAG>
 __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint32_t t_s, const uint32_t t_o,
                                              const int lim, const bool first, const uint32_t o_parity_prev,
-                                             const float scale_log2, float& m_run, float& m_used, float& l) {
+                                             const float scale_log2, float& m_run, float& m_used, float& l,
+                                             uint64_t* turn_bar, const uint32_t turn_parity, uint64_t* turn_out) {
     uint32_t v[4][32];
     tmem_ld32(t_s, v[0]);
     tmem_ld32(t_s + 32, v[1]);
@@ -373,6 +374,7 @@ __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint
         }
     }
     m_run = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+    if (turn_bar != nullptr && !wait_or_abort(sh, turn_bar, turn_parity)) return false;
     if (first) {
         m_used = m_run;  // finite: key 0 of the sequence is visible to every row and sits in the first tile
     } else {
@@ -417,6 +419,10 @@ __device__ __forceinline__ bool softmax_tile(Shared* sh, const int x, const uint
             v[c][i + 1] = pack_bf16(e2, e3);
         }
         tmem_st16(t_s + c * 16, v[c]);
+        if (c == 3 && turn_out != nullptr) {
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(turn_out);
+        }
         if (c & 1) {  // a half of P (64 keys) is complete: release its four P.V k-steps
             tmem_wait_st();
             tc_fence_before();
@@ -557,7 +563,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     for (int ks = half * 4; ks < half * 4 + 4; ++ks)
                         mma_ts(o_t, s_t + ks * 8, vd + (uint32_t)((ks * 16 * 128) >> 4), kIdescPV, (j > 0 || ks > 0));
                 }
-                tc_commit(&sh->o_full[x]);
                 ++tiles;
                 return true;
             };
@@ -584,18 +589,22 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int j = 0; ok && j < it.n_kv; ++j) {
                     const uint32_t vpos = 2 * (kt + j) + 1, kpos = vpos + 1;  // ring positions of V(j) and K(j+1)
                     if (!(ok = slot_full(vpos))) break;
+                    if (j + 1 < it.n_kv && !(ok = slot_full(kpos))) break;
                     if (j < n_x) {
                         if (!(ok = issue_pv(j, v_desc0 + (vpos % kSlots) * kSlotStep))) break;
-                        tc_commit(&sh->kv_empty[vpos % kSlots]);
+                        if (!(j + 1 < n_x)) {
+                            tc_commit(&sh->o_full[x]);
+                            tc_commit(&sh->kv_empty[vpos % kSlots]);
+                        }
                     } else {
                         mbar_arrive(&sh->kv_empty[vpos % kSlots]);
                     }
                     if (j + 1 < it.n_kv) {
-                        if (!(ok = slot_full(kpos))) break;
                         if (j + 1 < n_x) {
-                            tc_fence_after();
                             issue_qk(k_desc0 + (kpos % kSlots) * kSlotStep);
                             tc_commit(&sh->kv_empty[kpos % kSlots]);
+                            tc_commit(&sh->o_full[x]);
+                            tc_commit(&sh->kv_empty[vpos % kSlots]);
                             if (j + 2 == n_x) tc_commit(&sh->q_empty);  // this tile's last Q.K^T has been issued
                         } else {
                             mbar_arrive(&sh->kv_empty[kpos % kSlots]);
@@ -641,8 +650,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 constexpr bool kDiag = decltype(diag)::value;
                 if (!wait_or_abort(sh, &sh->s_full[x], tiles & 1u)) return false;
                 // A(j) starts after B(j-1); B(j) starts after A(j) while A still has tiles.
+                uint64_t* turn_bar = nullptr;
+                const uint32_t turn_parity = turns_seen & 1u;
                 if (both && (x == 0 ? j >= 1 : j < it.n_a)) {
-                    if (!wait_or_abort(sh, &sh->turn[x ^ 1], turns_seen & 1u)) return false;
+                    turn_bar = &sh->turn[x ^ 1];
                     ++turns_seen;
                 }
                 tc_fence_after();
@@ -670,13 +681,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     }
                 }
                 if (!softmax_tile<kDiag>(sh, x, t_s, t_o, kDiag ? first_lim - j * kTileKV + row : 0, j == 0,
-                                         (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l))
+                                         (tiles - 1) & 1u, p.scale_log2, m_run, m_used, l, turn_bar, turn_parity,
+                                         (both && (x == 0 || j + 1 < it.n_a)) ? &sh->turn[x] : nullptr))
                     return false;
                 // hand the turn over: A after each of its tiles, B while A still has a tile that will wait for it
-                if (both && (x == 0 || j + 1 < it.n_a)) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->turn[x]);
-                }
                 ++tiles;
                 return true;
             };
