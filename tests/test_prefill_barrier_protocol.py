@@ -1,6 +1,6 @@
 """Event-driven CPU model of the mbarrier protocol of the prefill kernel (csrc/varlen_prefill.cu).
 
-The kernel's five roles -- TMA producer, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
+The kernel's six roles -- K/V producer, Q loader, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
 waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
 lists under randomised latencies and checks what the hardware cannot tell us without a hang:
 
@@ -101,12 +101,13 @@ class Sim:
             raise ProtocolError(f"deadlock: {sorted(self.threads)} never finished")
 
 
-def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
+def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token_across_items=True):
     """items: per work item (n_a, n_b[, ragged]) = K/V tiles Q tile A / B visit (n_b = 0: no second tile) and whether
     the last V tile reaches past the sequence's end (the softmax warpgroups that use it zero those rows first)."""
     items = [it if len(it) == 3 else (it[0], it[1], False) for it in items]
     sim = Sim(seed, jitter)
-    q_full, q_empty = Bar("q_full", 1), Bar("q_empty", 2)
+    q_full = [Bar(f"q_full{x}", 1) for x in range(2)]
+    q_empty = [Bar(f"q_empty{x}", 1) for x in range(2)]
     kv_full = [Bar(f"kv_full{s}", 1) for s in range(SLOTS)]
     kv_empty = [Bar(f"kv_empty{s}", empty_count) for s in range(SLOTS)]
     s_full = [Bar(f"s_full{x}", 1) for x in range(2)]
@@ -120,10 +121,7 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
 
     def producer():
         kt = 0
-        for i, (n_a, n_b, _) in enumerate(items):
-            if i > 0:
-                yield ("wait", q_empty, i - 1)
-            yield ("tma", q_full)
+        for n_a, n_b, _ in items:
             for _ in range(max(n_a, n_b)):
                 for kv in range(2):
                     pos = 2 * kt + kv
@@ -136,6 +134,17 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                     slot_tile[s] = pos
                     yield ("tma", kv_full[s])
                 kt += 1
+
+    def q_loader():
+        used = [0, 0]
+        for n_a, n_b, _ in items:
+            for x, n_x in enumerate((n_a, n_b)):
+                if n_x == 0:
+                    continue
+                if used[x] > 0:
+                    yield ("wait", q_empty[x], used[x] - 1)
+                yield ("tma", q_full[x])
+                used[x] += 1
 
     def release(s):
         released[s] += 1
@@ -150,46 +159,53 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
 
         for i, (n_a, n_b, _) in enumerate(items):
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
-            yield ("wait", q_full, i)
-            if n_x == 0:
-                yield ("arrive", q_empty)
+            if n_x > 0:
+                yield ("wait", q_full[x], used)
             kpos = 2 * kt
             yield slot(kpos)
             if n_x > 0:
-                yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS]] + ([q_empty] if n_x == 1 else []))
+                yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS]] + ([q_empty[x]] if n_x == 1 else []))
             else:
                 yield ("arrive", kv_empty[kpos % SLOTS])
             release(kpos % SLOTS)
             for j in range(n_kv):
                 vpos, kpos = 2 * (kt + j) + 1, 2 * (kt + j) + 2
                 yield slot(vpos)
+                if j + 1 < n_kv:  # K(j+1) is awaited before P.V(j) so that nothing is polled between the two MMA groups
+                    yield slot(kpos)
                 if j < n_x:
                     if j == 0 and used > 0:
                         yield ("wait", o_empty[x], used - 1)
                     yield ("wait", p_full[x][0], tiles)
                     yield ("mma", 256, [])
                     yield ("wait", p_full[x][1], tiles)
-                    yield ("mma", 256, [o_full[x], kv_empty[vpos % SLOTS]])
+                    # the commits of P.V(j) follow the Q.K^T(j+1) MMAs when there are any
+                    yield ("mma", 256, [] if j + 1 < n_x else [o_full[x], kv_empty[vpos % SLOTS]])
                     tiles += 1
                 else:
                     yield ("arrive", kv_empty[vpos % SLOTS])
-                release(vpos % SLOTS)
                 if j + 1 < n_kv:
-                    yield slot(kpos)
                     if j + 1 < n_x:
-                        yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS]] + ([q_empty] if j + 2 == n_x else []))
+                        yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS], o_full[x], kv_empty[vpos % SLOTS]]
+                               + ([q_empty[x]] if j + 2 == n_x else []))
                     else:
                         yield ("arrive", kv_empty[kpos % SLOTS])
                     release(kpos % SLOTS)
+                release(vpos % SLOTS)
             used += 1 if n_x > 0 else 0
             kt += n_kv
 
     def softmax(x):
-        tiles = turns_seen = kt = 0
-        for n_a, n_b, ragged in items:
+        # The exponentials of all tiles of the CTA run one at a time in the order A(0) B(0) A(1) B(1) ... item after item:
+        # a tile waits for the other warpgroup's hand-over iff the slot before it belongs to the other warpgroup, and
+        # hands over iff the slot after it does.
+        tiles = turns_seen = kt = prev_nb = 0
+        for i, (n_a, n_b, ragged) in enumerate(items):
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
             kt0, kt = kt, kt + n_kv
             both = n_b > 0
+            after_b, prev_nb = (prev_nb > 0 and token_across_items), n_b
+            has_next = i + 1 < len(items) and token_across_items
             for j in range(n_x):
                 yield ("wait", s_full[x], tiles)
                 if ragged and j == n_kv - 1:  # zero the rows past the sequence's end in V(last) before P is handed over
@@ -198,15 +214,16 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                     if slot_tile[vpos % SLOTS] != vpos:
                         raise ProtocolError(f"softmax{x} zeroes rows of ring position {slot_tile[vpos % SLOTS]}, not {vpos}")
                     yield ("delay", 60)
-                if both and (j >= 1 if x == 0 else j < n_a):  # A(j) after B(j-1); B(j) after A(j) while A has tiles
+                yield ("delay", 300)  # scores to registers, row max
+                if ((both if j >= 1 else after_b) if x == 0 else j < n_a):
                     yield ("wait", turn[x ^ 1], turns_seen)
                     turns_seen += 1
-                yield ("delay", 900)
+                yield ("delay", 800)
                 yield ("arrive", p_full[x][0])
                 yield ("delay", 600)
-                yield ("arrive", p_full[x][1])
-                if both and (x == 0 or j + 1 < n_a) and (hand_turn_back or x == 0):
+                if (both if x == 0 else (j + 1 < n_a or (j + 1 == n_x and has_next))) and (hand_turn_back or x == 0):
                     yield ("arrive", turn[x])
+                yield ("arrive", p_full[x][1])
                 tiles += 1
             if n_x > 0:
                 yield ("wait", o_full[x], tiles - 1)
@@ -214,6 +231,7 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
                 yield ("arrive", o_empty[x])
 
     sim.spawn("producer", producer())
+    sim.spawn("q_loader", q_loader())
     for x in range(2):
         sim.spawn(f"issuer{x}", issuer(x))
         sim.spawn(f"softmax{x}", softmax(x))
