@@ -9,14 +9,17 @@
 // prefix = len_k - len_q; the model runner attaches the tables on a prefix hit,
 // engine/model_runner.py:311-314).
 //
-// Work item = 256 consecutive query rows of one sequence for one query head, handled
-// as two 128-row Q tiles (A and B) that share every K/V tile they read.  A tiny plan
-// kernel turns cu_seqlens into the item list, longest causal span first; one
-// persistent CTA per SM takes items round-robin from that list (heavy ones first, so
-// the CTAs finish together), and the heads of one (sequence, row block) are
-// neighbours in the list so that the G heads of a kv head find each other's K/V
-// tiles in L2.  Tensor memory and barriers are set up once per CTA; the loads of the
-// next item are already in flight while the current one drains.
+// Work item = two 128-row Q tiles (A and B) that share every K/V tile they read.  When
+// the GQA group size is even the two tiles are the same 128 query rows of two q heads of
+// one kv head: both see the same keys, run the same number of K/V tiles and finish
+// together.  Otherwise they are two consecutive row blocks of one head (B then sees one
+// K/V tile more than A).  A tiny plan kernel turns cu_seqlens into the list of
+// (sequence, row block) pairs, longest causal span first; one persistent CTA per SM
+// takes items round-robin from that list (heavy ones first, so the CTAs finish
+// together), and the heads of one (sequence, row block) are neighbours in the list so
+// that the G heads of a kv head find each other's K/V tiles in L2.  Tensor memory and
+// barriers are set up once per CTA; the loads of the next item are already in flight
+// while the current one drains.
 //
 // Per CTA (12 warps = 3 warpgroups; the first gives registers away with setmaxnreg, the softmax
 // warpgroups take them):
@@ -28,7 +31,9 @@
 //   warps 1, 2  MMA issuers, one thread each for Q tile A and Q tile B: S = Q K^T
 //               (operands in shared memory) and O += P V (P read from tensor memory, V
 //               from shared memory, MN-major), M = N = 128, K = 16 per instruction;
-//               tcgen05.commit signals the mbarriers.  Warp 1 also owns the tensor-
+//               tcgen05.commit signals the mbarriers.  K(j+1) is awaited before P.V(j) is
+//               issued and all commits of the pair follow the Q.K^T(j+1) MMAs, so nothing
+//               is polled between the two groups of MMAs.  Warp 1 also owns the tensor-
 //               memory allocation (512 columns: S_A S_B O_A O_B).
 //   warps 4-7   softmax of tile A, warps 8-11 of tile B: one thread per query row holds
 //               its S row (128 scores) in registers, keeps the running max / sum (packed
@@ -36,11 +41,13 @@
 //               releases four P.V k-steps) and rescales O only when the max grew by more
 //               than 2^8 (exact: the stale max is carried into the final normalisation).
 //               Tiles strictly above the diagonal are skipped, the diagonal tile is
-//               masked element-wise.  The two warpgroups take turns (A(0) B(0) A(1) ...):
-//               they share the four MUFU pipes, and alternating keeps one tile's MMAs
+//               masked element-wise.  The exponentials of the two tiles take turns
+//               (A(0) B(0) A(1) ...): they share the four MUFU pipes, which bound the
+//               kernel, and alternating keeps one tile's MMAs, score loads and row max
 //               running under the other tile's exponentials.
-// The three measures that only pay off together (each alone hits the next bottleneck at the same
-// level): two MMA issuers, the five-slot ring, and the softmax ping-pong.
+// Measures that only pay off together (each alone hits the next bottleneck at the same level): two
+// MMA issuers, the five-slot ring, the turn-taking, and -- later -- turn-taking for the exponentials
+// alone together with the poll-free MMA issue order.
 // Every mbarrier wait is bounded; on timeout the CTA raises a device error flag,
 // stops issuing work, and still releases its tensor memory before it exits.
 #include "common.cuh"
@@ -57,7 +64,7 @@ __device__ int g_error_flag = 0;
 
 constexpr int kD = 128;
 constexpr int kTileQ = 128;            // rows per Q tile
-constexpr int kBlockQ = 2 * kTileQ;    // rows per work item
+constexpr int kBlockQ = 2 * kTileQ;    // rows per work item when its two Q tiles are row blocks of one head
 constexpr int kTileKV = 128;
 constexpr int kThreads = 384;            // 3 warpgroups: {TMA, MMA, 2 idle warps} | softmax A | softmax B
 constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 dims bf16, 128B-swizzled
@@ -77,6 +84,7 @@ struct Params {
     int MB, block_size;
     __nv_bfloat16* out;
     int H, G;
+    int pair_heads;  // 1: an item is 128 rows of heads (2h, 2h+1); 0: 256 rows of one head
     float scale_log2;
 };
 
@@ -219,12 +227,13 @@ constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) 
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);  // B operand MN-major
 
 // ------------------------------------------------------------------------------------------
-// plan kernel: (sequence, 256-row block) pairs sorted by block index, largest first
+// plan kernel: (sequence, row block) pairs sorted by causal span, largest first
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens,
                                                             const int32_t* __restrict__ cu_k, int paged, int B,
-                                                            int4* __restrict__ items, int capacity) {
-    // A row block's weight is its causal span in 256-key units: level = prefix / 256 + block index.
+                                                            int4* __restrict__ items, int capacity, int bq) {
+    // bq = query rows per block (256, or 128 when an item is two heads).  A row block's weight is its causal span in
+    // bq-key units: level = prefix / bq + block index.
     __shared__ int hist[kMaxLevels];
     __shared__ int base[kMaxLevels];
     __shared__ int max_level, bad;
@@ -238,8 +247,8 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
         const int len_k = cu_k[b + 1] - cu_k[b];
         // keys can never be fewer than queries; packed keys sit beside the queries, so the counts must be equal
         if (len > 0 && (len_k < len || (!paged && (len_k != len || cu_k[b] != cu_seqlens[b])))) bad = 1;
-        const int lvl0 = len_k > len ? (len_k - len) / kBlockQ : 0;
-        const int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
+        const int lvl0 = len_k > len ? (len_k - len) / bq : 0;
+        const int n = len > 0 ? (len + bq - 1) / bq : 0;
         for (int l = 0; l < n; ++l) {
             int lvl = lvl0 + l;
             if (lvl >= kMaxLevels) {
@@ -271,13 +280,13 @@ __global__ void __launch_bounds__(1024) prefill_plan_kernel(const int32_t* __res
         const int start = cu_seqlens[b];
         const int len = cu_seqlens[b + 1] - start;
         const int len_k = cu_k[b + 1] - cu_k[b];
-        const int lvl0 = len_k > len ? (len_k - len) / kBlockQ : 0;
-        const int n = len > 0 ? (len + kBlockQ - 1) / kBlockQ : 0;
+        const int lvl0 = len_k > len ? (len_k - len) / bq : 0;
+        const int n = len > 0 ? (len + bq - 1) / bq : 0;
         for (int l = 0; l < n; ++l) {
             const int lvl = min(lvl0 + l, kMaxLevels - 1);
             const int slot = atomicAdd(&base[lvl], 1);
             if (slot < capacity) {
-                items[1 + 2 * slot] = make_int4(start, len, l * kBlockQ, b);
+                items[1 + 2 * slot] = make_int4(start, len, l * bq, b);
                 items[2 + 2 * slot] = make_int4(cu_k[b], len_k, 0, 0);
             }
         }
@@ -297,6 +306,7 @@ struct Shared {
 };
 
 __device__ __forceinline__ bool wait_or_abort(Shared* sh, uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
     if (sh->abort_flag) return false;
     if (mbar_wait(bar, parity)) return true;
     sh->abort_flag = 1;
@@ -307,14 +317,18 @@ __device__ __forceinline__ bool wait_or_abort(Shared* sh, uint64_t* bar, uint32_
 struct Item {
     int seq_start, len, q0, head, b;  // first query token of the sequence, query length, first row of the block
     int k_start, len_k, prefix;       // first key token (packed keys), key length, len_k - len
+    int dq, dh;          // Q tile B = rows + dq of head + dh
     int n_a, n_b, n_kv;  // KV tiles seen by Q tile A, by Q tile B (0: no such rows; else n_a or n_a + 1), and the larger
     bool ragged;         // the last KV tile reaches past the sequence's last key
 };
 
 __device__ __forceinline__ Item load_item(const Params& p, int idx) {
     Item it;
-    const int pair = idx / p.H;
-    it.head = idx - pair * p.H;
+    const int per_pair = p.pair_heads ? p.H >> 1 : p.H;
+    const int pair = idx / per_pair;
+    it.head = (idx - pair * per_pair) << p.pair_heads;
+    it.dq = p.pair_heads ? 0 : kTileQ;
+    it.dh = p.pair_heads;
     const int4 r = __ldg(p.items + 1 + 2 * pair), rk = __ldg(p.items + 2 + 2 * pair);
     it.seq_start = r.x;
     it.len = r.y;
@@ -323,11 +337,12 @@ __device__ __forceinline__ Item load_item(const Params& p, int idx) {
     it.k_start = rk.x;
     it.len_k = rk.y;
     it.prefix = it.len_k - it.len;  // >= 0: the plan kernel publishes no items otherwise
-    const int rows = min(kBlockQ, it.len - it.q0);
+    const int rows = min(p.pair_heads ? kTileQ : kBlockQ, it.len - it.q0);
     const int nk_total = (it.len_k + kTileKV - 1) / kTileKV;
     // the last row of Q tile x sees keys 0 .. prefix + q0 + 128 x + 127
     it.n_a = min(nk_total, (it.prefix + it.q0 + kTileQ - 1) / kTileKV + 1);
-    it.n_b = rows > kTileQ ? min(nk_total, (it.prefix + it.q0 + 2 * kTileQ - 1) / kTileKV + 1) : 0;
+    it.n_b = p.pair_heads ? it.n_a
+                          : (rows > kTileQ ? min(nk_total, (it.prefix + it.q0 + 2 * kTileQ - 1) / kTileKV + 1) : 0);
     it.n_kv = max(it.n_a, it.n_b);
     it.ragged = it.n_kv * kTileKV > it.len_k;
     return it;
@@ -343,7 +358,8 @@ __device__ __forceinline__ int kv_tile_token(const Params& p, const Item& it, in
 }
 
 // One 128-column S row -> running max, optional O rescale, bf16 P in two halves.  DIAG: key column c of this tile is
-// visible iff c <= lim (lim may be negative -- nothing visible in this tile -- or >= 127).
+// visible iff c <= lim (lim may be negative -- nothing visible in this tile -- or >= 127).  turn_bar (or null): the
+// other tile's hand-over this tile's exponentials wait for; turn_out (or null): where this tile hands over.
 // The whole row is held in registers (the softmax warpgroups raise their register budget with setmaxnreg), so
 // tensor memory is read once and its latency is paid once per tile.
 template <bool DIAG>
@@ -484,7 +500,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     // Register budget: the TMA / MMA warpgroup keeps 96 registers per thread, the two softmax warpgroups take 200
     // (96*128 + 200*256 <= 64K), enough to hold a whole 128-column score row.
-    const int total = (tmem != 0xFFFFFFFFu) ? p.items[0].x * p.H : 0;
+    const int total = (tmem != 0xFFFFFFFFu) ? p.items[0].x * (p.pair_heads ? p.H >> 1 : p.H) : 0;
     const int first_idx = blockIdx.x, stride = gridDim.x;
 
     if (warp < 4) {
@@ -504,8 +520,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tma_load_3d(sQ, &tm_q, &sh->q_full, 0, it.head, tok_q);
                 tma_load_3d(sQ + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q);
                 if (it.n_b > 0) {
-                    tma_load_3d(sQ + kTileBytes, &tm_q, &sh->q_full, 0, it.head, tok_q + kTileQ);
-                    tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, it.head, tok_q + kTileQ);
+                    tma_load_3d(sQ + kTileBytes, &tm_q, &sh->q_full, 0, it.head + it.dh, tok_q + it.dq);
+                    tma_load_3d(sQ + kTileBytes + kPanelBytes, &tm_q, &sh->q_full, 64, it.head + it.dh, tok_q + it.dq);
                 }
                 for (int j = 0; j < it.n_kv; ++j, ++kt) {
                     const int tok = kv_tile_token(p, it, j);
@@ -628,8 +644,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         uint32_t tiles = 0;  // tiles finished by this Q tile over all items (barrier phases)
         // Ping-pong between the two softmax warpgroups.  Both tiles' exponentials go through the same four MUFU
         // pipes; if both warpgroups exponentiate at once each takes twice as long and afterwards both tiles' MMAs
-        // queue up behind one another.  Inside an item with both tiles active the softmaxes therefore alternate
-        // A(0) B(0) A(1) B(1) ..., so that one tile's MMAs run under the other tile's softmax.
+        // queue up behind one another.  Inside an item with both tiles active the exponentials therefore alternate
+        // A(0) B(0) A(1) B(1) ...: a warpgroup loads its scores and finds the row max while the other one still
+        // exponentiates, takes the turn, and hands it over once its last chunk of P is on its way to tensor memory.
         uint32_t turns_seen = 0;  // completions of the other tile's turn barrier this warp has consumed
         uint32_t kt = 0;          // K/V tiles of the items before this one (ring positions)
         bool ok = true;
@@ -640,8 +657,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             kt += it.n_kv;
             if (n_x == 0) continue;
             const bool both = it.n_b > 0;
-            const int q_pos = it.q0 + x * kTileQ + row;             // row of the sequence's query block
-            const int first_lim = it.prefix + it.q0 + x * kTileQ;  // last key visible to the first row of this Q tile
+            const int q_pos = it.q0 + x * it.dq + row;             // row of the sequence's query block
+            const int first_lim = it.prefix + it.q0 + x * it.dq;  // last key visible to the first row of this Q tile
             float m_run = -INFINITY, m_used = -INFINITY, l = 0.f;
             // One KV tile of this Q tile.  Tiles whose last key the tile's first row may still see need no mask; the
             // one or two after them (one when the prefix is a multiple of the tile) are masked per element.  The two
@@ -697,7 +714,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             if (!(ok = wait_or_abort(sh, &sh->o_full[x], (tiles - 1) & 1u))) break;
             tc_fence_after();
             const float inv = 1.0f / l;
-            __nv_bfloat16* orow = p.out + ((size_t)(it.seq_start + q_pos) * p.H + it.head) * kD;
+            __nv_bfloat16* orow = p.out + ((size_t)(it.seq_start + q_pos) * p.H + it.head + x * it.dh) * kD;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t ov[32];
@@ -761,7 +778,7 @@ static int ensure_attr() {
     return NVLLM_B200_OK;
 }
 
-static int64_t item_capacity(int64_t T, int B) { return T / kBlockQ + B + 1; }
+static int64_t item_capacity(int64_t T, int B) { return T / kTileQ + B + 1; }  // covers 128-row blocks
 
 // Common launcher.  kv_tokens: extent of the token axis of k / v (T for packed tensors, the slot count of the cache).
 static int launch(const char* who, const void* q, const void* k, const void* v, int64_t kv_tokens,
@@ -785,7 +802,12 @@ static int launch(const char* who, const void* q, const void* k, const void* v, 
         return fail(NVLLM_B200_EWORKSPACE, "%s: workspace of %zu bytes required, got %zu", who, need,
                     workspace ? workspace_bytes : (size_t)0);
 
-    // Upper bound of (sequence, 256-row block) pairs: exact from the host copy of cu_seqlens, else from max_seqlen.
+    // Two q heads of one kv head make an item when there are such pairs: both Q tiles then see the same number of K/V
+    // tiles and finish together.  Otherwise an item is 256 rows of one head.
+    const int pair_heads = ((H / KVH) % 2 == 0) ? 1 : 0;
+    const int bq = pair_heads ? kTileQ : kBlockQ;
+    const int per_pair = pair_heads ? H / 2 : H;
+    // Upper bound of (sequence, row block) pairs: exact from the host copy of cu_seqlens, else from max_seqlen.
     int64_t pairs = 0;
     const int64_t cap = item_capacity(T, B);
     if (cu_seqlens_host) {
@@ -793,20 +815,20 @@ static int launch(const char* who, const void* q, const void* k, const void* v, 
             const int64_t len = (int64_t)cu_seqlens_host[b + 1] - cu_seqlens_host[b];
             if (len < 0 || cu_seqlens_host[b + 1] > T)
                 return fail(NVLLM_B200_EINVAL, "%s: cu_seqlens_host is not a non-decreasing prefix of T", who);
-            if (len > (int64_t)kMaxLevels * kBlockQ)
+            if (len > (int64_t)kMaxLevels * bq)
                 return fail(NVLLM_B200_EUNSUPPORTED, "%s: sequence of %lld tokens (max %d)", who, (long long)len,
-                            kMaxLevels * kBlockQ);
-            pairs += (len + kBlockQ - 1) / kBlockQ;
+                            kMaxLevels * bq);
+            pairs += (len + bq - 1) / bq;
         }
     } else {
         if (max_seqlen <= 0) return fail(NVLLM_B200_EINVAL, "%s: max_seqlen must be positive", who);
-        if (max_seqlen > kMaxLevels * kBlockQ)
-            return fail(NVLLM_B200_EUNSUPPORTED, "%s: max_seqlen %d (max %d)", who, max_seqlen, kMaxLevels * kBlockQ);
-        pairs = (int64_t)B * ((max_seqlen + kBlockQ - 1) / kBlockQ);
+        if (max_seqlen > kMaxLevels * bq)
+            return fail(NVLLM_B200_EUNSUPPORTED, "%s: max_seqlen %d (max %d)", who, max_seqlen, kMaxLevels * bq);
+        pairs = (int64_t)B * ((max_seqlen + bq - 1) / bq);
     }
     if (pairs > cap) pairs = cap;
     if (pairs == 0) return NVLLM_B200_OK;
-    if (pairs * H > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "%s: grid too large", who);
+    if (pairs * per_pair > 0x7fffffffLL) return fail(NVLLM_B200_EUNSUPPORTED, "%s: grid too large", who);
 
     int rc = ensure_attr();
     if (rc) return rc;
@@ -823,6 +845,7 @@ static int launch(const char* who, const void* q, const void* k, const void* v, 
     p.out = (__nv_bfloat16*)out;
     p.H = H;
     p.G = H / KVH;
+    p.pair_heads = pair_heads;
     p.scale_log2 = scale * 1.4426950408889634f;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -836,8 +859,8 @@ static int launch(const char* who, const void* q, const void* k, const void* v, 
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, prefill_plan_kernel, cu_seqlens_q, cu_seqlens_k, block_tables ? 1 : 0, B,
-                                     (int4*)workspace, (int)cap));
-    const int64_t ctas = pairs * H < (int64_t)sm_count() ? pairs * H : (int64_t)sm_count();
+                                     (int4*)workspace, (int)cap, bq));
+    const int64_t ctas = pairs * per_pair < (int64_t)sm_count() ? pairs * per_pair : (int64_t)sm_count();
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = kSmemBytes;

@@ -1,6 +1,6 @@
 """Event-driven CPU model of the mbarrier protocol of the prefill kernel (csrc/varlen_prefill.cu).
 
-The kernel's six roles -- K/V producer, Q loader, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
+The kernel's five roles -- TMA producer, two MMA issuers, two softmax warpgroups -- only meet through mbarriers whose
 waits see one parity bit.  The model replays their exact sequence of waits / arrivals / tcgen05.commit for random item
 lists under randomised latencies and checks what the hardware cannot tell us without a hang:
 
@@ -101,13 +101,12 @@ class Sim:
             raise ProtocolError(f"deadlock: {sorted(self.threads)} never finished")
 
 
-def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token_across_items=True):
+def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True):
     """items: per work item (n_a, n_b[, ragged]) = K/V tiles Q tile A / B visit (n_b = 0: no second tile) and whether
     the last V tile reaches past the sequence's end (the softmax warpgroups that use it zero those rows first)."""
     items = [it if len(it) == 3 else (it[0], it[1], False) for it in items]
     sim = Sim(seed, jitter)
-    q_full = [Bar(f"q_full{x}", 1) for x in range(2)]
-    q_empty = [Bar(f"q_empty{x}", 1) for x in range(2)]
+    q_full, q_empty = Bar("q_full", 1), Bar("q_empty", 2)
     kv_full = [Bar(f"kv_full{s}", 1) for s in range(SLOTS)]
     kv_empty = [Bar(f"kv_empty{s}", empty_count) for s in range(SLOTS)]
     s_full = [Bar(f"s_full{x}", 1) for x in range(2)]
@@ -121,7 +120,10 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
 
     def producer():
         kt = 0
-        for n_a, n_b, _ in items:
+        for i, (n_a, n_b, _) in enumerate(items):
+            if i > 0:
+                yield ("wait", q_empty, i - 1)
+            yield ("tma", q_full)
             for _ in range(max(n_a, n_b)):
                 for kv in range(2):
                     pos = 2 * kt + kv
@@ -134,17 +136,6 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
                     slot_tile[s] = pos
                     yield ("tma", kv_full[s])
                 kt += 1
-
-    def q_loader():
-        used = [0, 0]
-        for n_a, n_b, _ in items:
-            for x, n_x in enumerate((n_a, n_b)):
-                if n_x == 0:
-                    continue
-                if used[x] > 0:
-                    yield ("wait", q_empty[x], used[x] - 1)
-                yield ("tma", q_full[x])
-                used[x] += 1
 
     def release(s):
         released[s] += 1
@@ -159,12 +150,13 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
 
         for i, (n_a, n_b, _) in enumerate(items):
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
-            if n_x > 0:
-                yield ("wait", q_full[x], used)
+            yield ("wait", q_full, i)
+            if n_x == 0:
+                yield ("arrive", q_empty)
             kpos = 2 * kt
             yield slot(kpos)
             if n_x > 0:
-                yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS]] + ([q_empty[x]] if n_x == 1 else []))
+                yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS]] + ([q_empty] if n_x == 1 else []))
             else:
                 yield ("arrive", kv_empty[kpos % SLOTS])
             release(kpos % SLOTS)
@@ -187,7 +179,7 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
                 if j + 1 < n_kv:
                     if j + 1 < n_x:
                         yield ("mma", 512, [s_full[x], kv_empty[kpos % SLOTS], o_full[x], kv_empty[vpos % SLOTS]]
-                               + ([q_empty[x]] if j + 2 == n_x else []))
+                               + ([q_empty] if j + 2 == n_x else []))
                     else:
                         yield ("arrive", kv_empty[kpos % SLOTS])
                     release(kpos % SLOTS)
@@ -196,16 +188,11 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
             kt += n_kv
 
     def softmax(x):
-        # The exponentials of all tiles of the CTA run one at a time in the order A(0) B(0) A(1) B(1) ... item after item:
-        # a tile waits for the other warpgroup's hand-over iff the slot before it belongs to the other warpgroup, and
-        # hands over iff the slot after it does.
-        tiles = turns_seen = kt = prev_nb = 0
-        for i, (n_a, n_b, ragged) in enumerate(items):
+        tiles = turns_seen = kt = 0
+        for n_a, n_b, ragged in items:
             n_x, n_kv = (n_a, n_b)[x], max(n_a, n_b)
             kt0, kt = kt, kt + n_kv
             both = n_b > 0
-            after_b, prev_nb = (prev_nb > 0 and token_across_items), n_b
-            has_next = i + 1 < len(items) and token_across_items
             for j in range(n_x):
                 yield ("wait", s_full[x], tiles)
                 if ragged and j == n_kv - 1:  # zero the rows past the sequence's end in V(last) before P is handed over
@@ -214,15 +201,15 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
                     if slot_tile[vpos % SLOTS] != vpos:
                         raise ProtocolError(f"softmax{x} zeroes rows of ring position {slot_tile[vpos % SLOTS]}, not {vpos}")
                     yield ("delay", 60)
-                yield ("delay", 300)  # scores to registers, row max
-                if ((both if j >= 1 else after_b) if x == 0 else j < n_a):
+                yield ("delay", 300)  # scores to registers, row max: not exclusive
+                if both and (j >= 1 if x == 0 else j < n_a):  # A(j) after B(j-1); B(j) after A(j) while A has tiles
                     yield ("wait", turn[x ^ 1], turns_seen)
                     turns_seen += 1
                 yield ("delay", 800)
                 yield ("arrive", p_full[x][0])
                 yield ("delay", 600)
-                if (both if x == 0 else (j + 1 < n_a or (j + 1 == n_x and has_next))) and (hand_turn_back or x == 0):
-                    yield ("arrive", turn[x])
+                if both and (x == 0 or j + 1 < n_a) and (hand_turn_back or x == 0):
+                    yield ("arrive", turn[x])  # handed over once the last chunk of P is on its way
                 yield ("arrive", p_full[x][1])
                 tiles += 1
             if n_x > 0:
@@ -231,7 +218,6 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
                 yield ("arrive", o_empty[x])
 
     sim.spawn("producer", producer())
-    sim.spawn("q_loader", q_loader())
     for x in range(2):
         sim.spawn(f"issuer{x}", issuer(x))
         sim.spawn(f"softmax{x}", softmax(x))
@@ -239,14 +225,20 @@ def run_cta(items, seed=0, jitter=0.0, empty_count=2, hand_turn_back=True, token
     return sim.t
 
 
-def item_tiles(q0, rows, prefix=0, last=None):
-    """What load_item computes for the 256-row block starting at row q0 with `rows` live rows of a sequence with
-    `prefix` cached tokens; `last` says whether it is the sequence's final block (default: iff rows < 256)."""
-    last = rows < 256 if last is None else last
+def item_tiles(q0, rows, prefix=0, last=None, pair_heads=False):
+    """What load_item computes for the row block starting at row q0 with `rows` live rows of a sequence with
+    `prefix` cached tokens; `last` says whether it is the sequence's final block (default: iff the block is not full).
+    pair_heads: the item is 128 rows of two heads (both Q tiles see the same keys) instead of 256 rows of one head."""
+    full = 128 if pair_heads else 256
+    rows = min(rows, full)
+    last = rows < full if last is None else last
     len_k = prefix + q0 + rows if last else prefix + q0 + rows + 300
     nk_total = -(-len_k // 128)
     n_a = min(nk_total, (prefix + q0 + 127) // 128 + 1)
-    n_b = min(nk_total, (prefix + q0 + 255) // 128 + 1) if rows > 128 else 0
+    if pair_heads:
+        n_b = n_a
+    else:
+        n_b = min(nk_total, (prefix + q0 + 255) // 128 + 1) if rows > 128 else 0
     return n_a, n_b, max(n_a, n_b) * 128 > len_k
 
 
@@ -254,13 +246,16 @@ def test_single_items_of_every_shape():
     for q0 in (0, 256, 1024):
         for rows in (1, 128, 129, 256):
             assert run_cta([item_tiles(q0, rows)]) > 0
+            assert run_cta([item_tiles(q0, rows, pair_heads=True)]) > 0
 
 
 @pytest.mark.parametrize("seed", range(40))
 def test_random_item_lists_under_random_latencies(seed):
     rng = random.Random(seed)
-    items = [item_tiles(256 * rng.randint(0, 7), rng.choice([1, 64, 128, 129, 200, 256, 256, 256]),
-                        prefix=rng.choice([0, 0, 1, 127, 128, 300]), last=rng.choice([None, None, True]))
+    pair_heads = seed % 2 == 1
+    items = [item_tiles((128 if pair_heads else 256) * rng.randint(0, 7), rng.choice([1, 64, 128, 129, 200, 256, 256, 256]),
+                        prefix=rng.choice([0, 0, 1, 127, 128, 300]), last=rng.choice([None, None, True]),
+                        pair_heads=pair_heads)
              for _ in range(rng.randint(1, 14))]
     for jitter in (0.0, 0.4, 0.95):
         run_cta(items, seed=seed, jitter=jitter)
