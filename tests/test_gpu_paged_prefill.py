@@ -64,12 +64,14 @@ def _status_clean():
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("h,kvh", [(8, 2), (3, 1)])
 @pytest.mark.parametrize("prefix", [0, 1, 255, 256, 257, 3 * 256 + 17])
-def test_prefix_lengths_with_ragged_new_lengths(prefix):
-    """Every sequence of the batch has the same cached prefix; the new lengths straddle the 128 / 256 row tiles."""
+def test_prefix_lengths_with_ragged_new_lengths(prefix, h, kvh):
+    """Every sequence of the batch has the same cached prefix; the new lengths straddle the 128 / 256 row tiles.
+    (8, 2): an item is 128 rows of two heads; (3, 1): the group size is odd, an item is 256 rows of one head."""
     new_lens = [1, 5, 127, 128, 129, 255, 256, 257, 300, 700]
-    c = _case([prefix] * len(new_lens), new_lens, h=8, kvh=2, block_size=256, seed=600 + prefix)
-    assert_attention_close(torch_to_f32(_run(c)), _want(c), f"prefix {prefix}")
+    c = _case([prefix] * len(new_lens), new_lens, h=h, kvh=kvh, block_size=256, seed=600 + prefix + h)
+    assert_attention_close(torch_to_f32(_run(c)), _want(c), f"prefix {prefix} H={h} KVH={kvh}")
     _status_clean()
 
 
@@ -83,7 +85,7 @@ def test_mixed_prefixes_block_128_and_grid_from_max_seqlen():
     _status_clean()
 
 
-@pytest.mark.parametrize("h,kvh", [(4, 4), (8, 1), (32, 8)])
+@pytest.mark.parametrize("h,kvh", [(4, 4), (8, 1), (32, 8), (6, 2)])
 def test_head_ratios(h, kvh):
     c = _case([200, 0, 333], [260, 140, 31], h=h, kvh=kvh, block_size=256, seed=620 + h)
     assert_attention_close(torch_to_f32(_run(c)), _want(c), f"H={h} KVH={kvh}")

@@ -44,6 +44,15 @@ def test_ragged_lengths_around_tile_edges(lens):
     _status_clean()
 
 
+@pytest.mark.parametrize("h,kvh", [(2, 2), (6, 2)])
+@pytest.mark.parametrize("lens", [[1], [128], [129], [256], [257], [511, 1, 130], [64, 700, 3, 256, 385]])
+def test_ragged_lengths_with_odd_group_sizes(lens, h, kvh):
+    """An odd GQA group size makes a work item 256 rows of one head instead of 128 rows of two heads."""
+    got, want, _ = _run_case(lens, h=h, kvh=kvh, seed=7 + sum(lens) + h)
+    assert_attention_close(got, want, f"lens={lens} H={h} KVH={kvh}")
+    _status_clean()
+
+
 @pytest.mark.parametrize("h,kvh", [(4, 4), (8, 4), (16, 4), (32, 8), (8, 1), (4, 1)])
 def test_gqa_ratios_and_head_shards(h, kvh):
     got, want, _ = _run_case([200, 513, 40], h=h, kvh=kvh, seed=50 + h + kvh)
