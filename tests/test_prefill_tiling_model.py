@@ -1,16 +1,17 @@
 """CPU model of the tile bookkeeping of the prefill kernel (csrc/varlen_prefill.cu): which 128-key tiles each 128-row
-Q tile of a 256-row work item visits, and the element mask on its last (diagonal) tile, must cover exactly the causal
+Q tile of a work item (256 rows of one head, or 128 rows of two heads when the GQA group size is even) visits, and the element mask on its last (diagonal) tile, must cover exactly the causal
 region -- key c is used for query position p iff c <= p -- for every sequence length; and the plan kernel's item list
 must contain every (sequence, row block) once, longest causal span first."""
 import numpy as np
 import pytest
 
 
-def visited(L, q0, x):
-    """Boolean [rows_of_tile, L_padded]: keys the kernel lets row r of Q tile x (0 = A, 1 = B) of the item at q0 see."""
-    rows = min(256, L - q0)
+def visited(L, q0, x, pair_heads=False):
+    """Boolean [rows_of_tile, L_padded]: keys the kernel lets row r of Q tile x (0 = A, 1 = B) of the item at q0 see.
+    pair_heads: both tiles are the rows q0 .. q0+127 (of two heads) and visit the same tiles."""
+    rows = min(128 if pair_heads else 256, L - q0)
     n_a = q0 // 128 + 1
-    n_b = q0 // 128 + 2 if rows > 128 else 0
+    n_b = n_a if pair_heads else (q0 // 128 + 2 if rows > 128 else 0)
     n_x = n_a if x == 0 else n_b
     width = (max(n_a, n_b)) * 128
     seen = np.zeros((128, width), dtype=bool)
@@ -35,6 +36,12 @@ def test_tiles_and_masks_cover_exactly_the_causal_region(L):
                 assert np.array_equal(seen[r], want), (L, q0, x, r)
         rows = min(256, L - q0)
         assert (rows > 128) == (visited(L, q0, 1)[1] > 0)
+    for q0 in range(0, L, 128):  # items of two heads: both tiles hold the same rows
+        for x in (0, 1):
+            seen, n_x = visited(L, q0, x, pair_heads=True)
+            assert n_x == q0 // 128 + 1
+            for r in range(min(128, L - q0)):
+                assert np.array_equal(seen[r], np.arange(seen.shape[1]) <= q0 + r), (L, q0, x, r)
 
 
 def test_plan_orders_items_longest_span_first():
