@@ -58,7 +58,7 @@ PREFILL_METRIC, PREFILL_UNIT = "varlen_prefill_tflops", "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (a property of the launch, independent of the page-pool size the capture used);
 # None where no capture exists.
-NCU_TRAFFIC_BYTES = {"cfg2": 1_021_858_480, "cfg4": 1_409_609_584}
+NCU_TRAFFIC_BYTES = {"cfg2": 1_021_858_480, "cfg4": 1_781_467_008}
 
 
 def load_peaks():
