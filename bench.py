@@ -574,6 +574,55 @@ class PrefillRig:
         from nanovllm_jax_b200 import ops
         ops.store_kvcache(self.k, self.v, self.kc.view(self.flat), self.vc.view(self.flat), self.slots)
 
+    # ---- the step before attention in a Qwen3 layer: q-norm, k-norm, rotary embedding, store (one pass) ----
+    def setup_pre_attention(self):
+        import torch
+        w, dev = self.w, self.dev
+        inv = 1.0 / (1e6 ** (torch.arange(0, w.head_dim, 2, device=dev, dtype=torch.float32) / w.head_dim))
+        ang = torch.arange(int(w.seq_lens.max()), device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos_sin = torch.cat([ang.cos(), ang.sin()], dim=-1).contiguous()
+        pos = np.concatenate([np.arange(n, dtype=np.int32) for n in w.seq_lens])
+        self.positions = torch.from_numpy(pos).to(dev)
+        self.q_w = torch.ones(w.head_dim, dtype=torch.float32, device=dev)
+        self.k_w = torch.ones(w.head_dim, dtype=torch.float32, device=dev)
+        self.q2, self.k2 = self.q.clone(), self.k.clone()  # rotated in place: the prefill's inputs stay as they are
+        t = w.total_tokens
+        self.pre_bytes = t * ((self.h + 2 * self.kvh) + (self.h + self.kvh) + 2 * self.kvh) * w.head_dim * 2
+
+    def pre_attention_only(self, i=0):
+        from nanovllm_jax_b200 import ops
+        ops.qk_norm_rope_store(self.q2, self.k2, self.v, self.q_w, self.k_w, self.cos_sin, self.positions,
+                               self.kc.view(self.flat), self.vc.view(self.flat), self.slots)
+
+    # ---- prefill over a cached prefix: the first half of every sequence is cached, the second half is new ----
+    def setup_prefix(self):
+        import torch
+        w, dev = self.w, self.dev
+        lens = w.seq_lens.astype(np.int64)
+        prefix = lens // 2
+        new = lens - prefix
+        self.store_only()  # every token's K/V row sits in the pages
+        width = max(len(b) for b in w.block_lists)
+        tables = np.full((w.batch, width), -1, np.int32)
+        for b, blocks in enumerate(w.block_lists):
+            tables[b, : len(blocks)] = blocks
+        self.tables = torch.from_numpy(tables).to(dev)
+        self.cu_q_host = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+        self.cu_q = torch.from_numpy(self.cu_q_host).to(dev)
+        self.cu_k = torch.from_numpy(w.cu_seqlens).to(dev)
+        self.max_new = int(new.max())
+        rows = np.concatenate([np.arange(w.cu_seqlens[b] + prefix[b], w.cu_seqlens[b + 1]) for b in range(w.batch)])
+        self.q_new = self.q[torch.from_numpy(rows).to(dev)].contiguous()
+        self.out_new = torch.empty_like(self.q_new)
+        self.prefix_flops = int(4 * w.head_dim * self.h * int((new * prefix + new * (new + 1) // 2).sum()))
+        self.prefix_desc = (f"{w.batch} sequences, {int(prefix.sum())} cached + {int(new.sum())} new tokens "
+                            f"(the second half of each sequence of the prefill workload)")
+
+    def prefix_prefill_only(self, i=0):
+        from nanovllm_jax_b200 import ops
+        return ops.paged_prefill(self.q_new, self.kc, self.vc, self.tables, self.cu_q, self.cu_k, self.max_new,
+                                 self.w.scale, self.w.block_size, out=self.out_new, cu_seqlens_host=self.cu_q_host)
+
 
 def prefill_roofline(rig, launches, warm):
     _, sustained, burst, kind = load_peaks()
@@ -630,6 +679,27 @@ def secondary_block(dev, rank, launches, warm):
                                          "frac": gbps / peak, "traffic": None,
                                          "note": "325 MB read + 325 MB written per launch; with back-to-back launches "
                                                  "part of the source rows is still in the 126 MB L2"}}
+    pr.setup_pre_attention()
+    pa_us, pa_pct = time_pass(pr.pre_attention_only, launches, warm)
+    gbps = pr.pre_bytes / (pa_us / 1e6) / 1e9
+    out["pre_attention"] = {"workload": f"q-norm + k-norm + rotary embedding + store of {pr.w.total_tokens} tokens, "
+                                        f"{pr.h} q heads / {pr.kvh} kv heads (one nvllm_b200_qk_norm_rope_store call)",
+                            "bytes_per_launch": pr.pre_bytes, "us_per_launch": pa_us,
+                            "us_per_launch_p10_p50_p90": pa_pct, "launches_timed": launches,
+                            "roofline": {"bound": "hbm", "achieved": gbps, "peak": peak, "unit": "GB/s",
+                                         "frac": gbps / peak, "traffic": None,
+                                         "note": "q, k, v read; q, k written back; rotated k and v scattered into the pages"}}
+    pr.setup_prefix()
+    n_l, n_w = max(10, launches // 2), max(3, warm // 2)
+    px_us, px_pct = time_pass(pr.prefix_prefill_only, n_l, n_w)
+    tfl = pr.prefix_flops / (px_us / 1e6) / 1e12
+    out["prefix_prefill"] = {"workload": pr.prefix_desc + ", keys and values read from the pages through block tables "
+                                         "(one nvllm_b200_paged_prefill call)",
+                             "flops_per_launch": pr.prefix_flops, "us_per_launch": px_us,
+                             "us_per_launch_p10_p50_p90": px_pct, "launches_timed": n_l,
+                             "roofline": {"bound": "tensor", "achieved": tfl, "peak": sustained, "unit": "TFLOP/s",
+                                          "frac": tfl / sustained, "frac_of_burst": tfl / burst, "peak_burst": burst,
+                                          "traffic": None}}
     del pr
     gc.collect()
     torch.cuda.empty_cache()

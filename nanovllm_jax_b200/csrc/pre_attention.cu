@@ -5,10 +5,20 @@
 namespace nvllm {
 namespace preattn {
 
-__global__ void __launch_bounds__(kThreads) pre_attention_kernel(const Params p) {
+// Persistent: the row blocks are dealt round-robin to a grid of a few CTAs per SM, and every thread has the loads of
+// kRowsInFlight rows in flight before it starts on the first one.
+__global__ void __launch_bounds__(kThreads, 2) pre_attention_kernel(const Params p, const int64_t blocks) {
     griddep_wait();  // q, k, v may come from the kernel just before this one (the QKV projection)
     griddep_launch_dependents();
-    pre_attention_block(blockIdx.x, p);
+    const int q = threadIdx.x & 3;
+    const int rb = threadIdx.x >> 2;
+    for (int64_t b0 = (int64_t)blockIdx.x * kRowsInFlight; b0 < blocks; b0 += (int64_t)gridDim.x * kRowsInFlight) {
+        Part c[kRowsInFlight];
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) c[u] = load_part((b0 + u) * kRowsPerBlock + rb, q, p);  // dead past the end
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) finish_part(c[u], q, p);
+    }
 }
 
 int check_args(const char* who, const void* q, const void* k, const void* v, const float* q_weight, const float* k_weight,
@@ -46,11 +56,14 @@ extern "C" int nvllm_b200_qk_norm_rope_store(void* q, void* k, const void* v, co
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)preattn::blocks_for(T, H, KVH));
+    const int64_t blocks = preattn::blocks_for(T, H, KVH);
+    const int64_t groups = (blocks + preattn::kRowsInFlight - 1) / preattn::kRowsInFlight;
+    const int64_t resident = (int64_t)sm_count() * 2;  // the launch bounds keep two CTAs of 256 threads on an SM
+    cfg.gridDim = dim3((unsigned)(groups < resident ? groups : resident));
     cfg.blockDim = dim3(preattn::kThreads);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, preattn::pre_attention_kernel, p));
+    NVLLM_CUDA_OK(cudaLaunchKernelEx(&cfg, preattn::pre_attention_kernel, p, blocks));
     return NVLLM_B200_OK;
 }

@@ -9,12 +9,14 @@
 // q and k are updated in place (prefill reads the packed k); k and v rows also go to their cache slots.
 //
 // HBM-bound: per token (H + 2 KVH) rows of 256 B are read once, the q and k rows written back, the k and v rows
-// written to the cache.  One half-warp per row, 16 bytes per lane; the rotation partner of lane l is lane l ^ 8.
+// written to the cache.  Four lanes per row, four 16-byte chunks per lane (chunks q, q+4, q+8, q+12 of the row's sixteen:
+// a dim and its rotation partner 64 dims further sit in the same lane, and three quarters of the per-row scalar work --
+// the divide and the square root -- that sixteen lanes per row repeated is gone).
 //
 // Arithmetic is pinned so that a host restatement reproduces the bf16 results bit for bit: every fp32 operation
 // is a separate IEEE round-to-nearest multiply / add / divide / square root (no fused multiply-add, no approximate
-// reciprocal square root), and the sum of squares runs in one fixed order: eight elements left to right inside a
-// lane, then a butterfly over the sixteen lanes of the row (xor 8, 4, 2, 1).
+// reciprocal square root), and the sum of squares runs in one fixed order: sixteen partial sums of eight elements
+// each, left to right, then a butterfly over the sixteen partial sums (index xor 8, 4, 2, 1).
 #pragma once
 
 #include "common.cuh"
@@ -24,7 +26,7 @@ namespace preattn {
 
 constexpr int kD = 128;
 constexpr int kThreads = 256;
-constexpr int kRowsPerBlock = kThreads / 16;
+constexpr int kRowsPerBlock = kThreads / 4;  // four lanes per 256-byte row
 
 struct Params {
     __nv_bfloat16* q;
@@ -61,75 +63,126 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+constexpr int kRowsInFlight = 2;  // rows a thread of the stand-alone kernel has loads in flight for
+
 inline int64_t blocks_for(int64_t T, int H, int KVH) {
     const int64_t rows = T * (H + 2 * KVH);
     return (rows + kRowsPerBlock - 1) / kRowsPerBlock;
 }
 
-// The share of block `block` (kThreads threads): rows [block * 16, block * 16 + 16) of the T * (H + 2 KVH) rows.
-__device__ __forceinline__ void pre_attention_block(int64_t block, const Params& p) {
+// A quarter of one row as a thread holds it between its loads and its math: lane q (0..3) of the row's four lanes owns
+// the 16-byte chunks q, q + 4, q + 8 and q + 12 (chunk c = dims 8c .. 8c+7).
+struct Part {
+    uint4 w[4];    // the four chunks (zeros for a dead row)
+    int64_t t;     // token
+    int64_t slot;  // cache slot (k and v rows), -1: none
+    int pos;       // position of the token
+    int r;         // row of the token: [0, H) q heads, [H, H+KVH) k heads, [H+KVH, H+2KVH) v heads
+    bool live;
+};
+
+// Issues the loads of lane q's part of row `row` (of the T * (H + 2 KVH) rows); nothing here waits for them.
+__device__ __forceinline__ Part load_part(int64_t row, const int q, const Params& p) {
+    Part c;
     const int rows_per_token = p.H + 2 * p.KVH;
-    const int64_t row = block * kRowsPerBlock + (threadIdx.x >> 4);  // one half-warp per row
-    const int l = threadIdx.x & 15;                                   // 16-byte chunk of the row
-    const bool live = row < p.T * rows_per_token;
-    const int64_t t = live ? row / rows_per_token : 0;
-    const int r = live ? (int)(row - t * rows_per_token) : 0;
-    // r in [0, H): q head; [H, H+KVH): k head; [H+KVH, H+2KVH): v head
-    const int kind = r < p.H ? 0 : (r < p.H + p.KVH ? 1 : 2);
-    const int head = kind == 0 ? r : (kind == 1 ? r - p.H : r - p.H - p.KVH);
-    const __nv_bfloat16* src = kind == 0 ? p.q + (t * p.H + head) * kD
-                                          : (kind == 1 ? p.k : p.v) + (t * p.KVH + head) * kD;
-    uint4 w = make_uint4(0, 0, 0, 0);
-    if (live) w = *reinterpret_cast<const uint4*>(src + l * 8);
-    const int64_t slot = live && kind != 0 ? (int64_t)__ldg(p.slot_mapping + t) : -1;
-    {   // every lane runs the math (full-warp shuffles; the two rows of a warp may be of different kinds);
-        // v rows and dead rows simply do not use the result
-        const uint4 w_in = w;
-        float x[8];
-        unpack8(w, x);
-        float ss = __fmul_rn(x[0], x[0]);
+    c.live = row < p.T * rows_per_token;
+    c.t = c.live ? row / rows_per_token : 0;
+    c.r = c.live ? (int)(row - c.t * rows_per_token) : 0;
+    const int kind = c.r < p.H ? 0 : (c.r < p.H + p.KVH ? 1 : 2);
+    const int head = kind == 0 ? c.r : (kind == 1 ? c.r - p.H : c.r - p.H - p.KVH);
+    const __nv_bfloat16* src = kind == 0 ? p.q + (c.t * p.H + head) * kD
+                                          : (kind == 1 ? p.k : p.v) + (c.t * p.KVH + head) * kD;
 #pragma unroll
-        for (int i = 1; i < 8; ++i) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
-        // butterfly over the 16 lanes of the row (xor offsets below 16 stay inside the half-warp); both partners
-        // compute the same sum, so every lane ends with the same value
+    for (int i = 0; i < 4; ++i) {
+        c.w[i] = make_uint4(0, 0, 0, 0);
+        if (c.live) c.w[i] = *reinterpret_cast<const uint4*>(src + (q + 4 * i) * 8);
+    }
+    c.slot = c.live && kind != 0 ? (int64_t)__ldg(p.slot_mapping + c.t) : -1;
+    c.pos = c.live ? __ldg(p.positions + c.t) : 0;
+    return c;
+}
+
+__device__ __forceinline__ void load8(const float* src, float (&f)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+
+// Norm, rotation and stores of one part.  Every lane of the warp must call this together (full-warp shuffles; the
+// eight rows of a warp may be of different kinds): v rows and dead rows simply do not use the result of the math.
+//
+// The sum of squares keeps one fixed order whatever the lane layout: sixteen partial sums, one per chunk, each taken
+// front to back, then the butterfly p[c] + p[c ^ 8], + [c ^ 4], + [c ^ 2], + [c ^ 1].  With chunks q, q+4, q+8, q+12
+// in one lane the first two levels are local and the last two are shuffles over the row's four lanes.
+__device__ __forceinline__ void finish_part(const Part& ch, const int q, const Params& p) {
+    const int kind = ch.r < p.H ? 0 : (ch.r < p.H + p.KVH ? 1 : 2);
+    const int head = kind == 0 ? ch.r : (kind == 1 ? ch.r - p.H : ch.r - p.H - p.KVH);
+    uint4 out[4];
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    for (int i = 0; i < 4; ++i) out[i] = ch.w[i];
+    // a warp whose eight rows are all v rows (or past the end) has nothing to compute: the rows are copied
+    if (!__all_sync(0xffffffffu, kind == 2 || !ch.live)) {
+        float x[4][8], pp[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            unpack8(ch.w[i], x[i]);
+            float ss = __fmul_rn(x[i][0], x[i][0]);
+#pragma unroll
+            for (int e = 1; e < 8; ++e) ss = __fadd_rn(ss, __fmul_rn(x[i][e], x[i][e]));
+            pp[i] = ss;
+        }
+        float ss = __fadd_rn(__fadd_rn(pp[0], pp[2]), __fadd_rn(pp[1], pp[3]));  // levels c ^ 8 and c ^ 4
+        ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 2));                  // level c ^ 2
+        ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, 1));                  // level c ^ 1
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, 1.0f / kD), p.eps)));
-        const float* wgt = (kind == 1 ? p.k_weight : p.q_weight) + l * 8;
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(wgt)), w1 = __ldg(reinterpret_cast<const float4*>(wgt) + 1);
-        const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-        float y[8], z[8];
+        const float* wgt = kind == 1 ? p.k_weight : p.q_weight;
+        float y[4][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = round_bf16(__fmul_rn(__fmul_rn(x[i], inv), ws[i]));  // the norm returns bf16
-        // rotation partner: dims d and d + 64 -> lanes l and l ^ 8
+        for (int i = 0; i < 4; ++i) {
+            float ws[8];
+            load8(wgt + (q + 4 * i) * 8, ws);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) z[i] = __shfl_xor_sync(0xffffffffu, y[i], 8);
-        int64_t pos = live ? (int64_t)__ldg(p.positions + t) : 0;
+            for (int e = 0; e < 8; ++e) y[i][e] = round_bf16(__fmul_rn(__fmul_rn(x[i][e], inv), ws[e]));  // the norm returns bf16
+        }
+        int64_t pos = ch.pos;
         if (pos < 0) pos = 0;
         if (pos >= p.max_pos) pos = p.max_pos - 1;
-        const float* cs = p.cos_sin + pos * kD + (l & 7) * 8;
-        const float4 c0 = __ldg(reinterpret_cast<const float4*>(cs)), c1 = __ldg(reinterpret_cast<const float4*>(cs) + 1);
-        const float4 s0 = __ldg(reinterpret_cast<const float4*>(cs + 64)), s1 = __ldg(reinterpret_cast<const float4*>(cs + 64) + 1);
-        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-        float o[8];
-        if (l < 8) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = __fsub_rn(__fmul_rn(y[i], c[i]), __fmul_rn(z[i], s[i]));  // x1 cos - x2 sin
-        } else {
+        for (int i = 0; i < 2; ++i) {  // chunk q + 4i holds dims d < 64, its rotation partner d + 64 is chunk q + 4i + 8
+            float c[8], sn[8], lo[8], hi[8];
+            const float* cs = p.cos_sin + pos * kD + (q + 4 * i) * 8;
+            load8(cs, c);
+            load8(cs + 64, sn);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = __fadd_rn(__fmul_rn(y[i], c[i]), __fmul_rn(z[i], s[i]));  // x2 cos + x1 sin
+            for (int e = 0; e < 8; ++e) {
+                lo[e] = __fsub_rn(__fmul_rn(y[i][e], c[e]), __fmul_rn(y[i + 2][e], sn[e]));  // x1 cos - x2 sin
+                hi[e] = __fadd_rn(__fmul_rn(y[i + 2][e], c[e]), __fmul_rn(y[i][e], sn[e]));  // x2 cos + x1 sin
+            }
+            out[i] = pack8(lo);
+            out[i + 2] = pack8(hi);
         }
-        w = kind == 2 ? w_in : pack8(o);
-        if (live && kind != 2) {
-            __nv_bfloat16* dst = kind == 0 ? p.q + (t * p.H + head) * kD : p.k + (t * p.KVH + head) * kD;
-            *reinterpret_cast<uint4*>(dst + l * 8) = w;
+        if (kind == 2) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = ch.w[i];
         }
     }
-    if (live && kind != 0 && slot >= 0 && slot < p.num_slots) {
-        __nv_bfloat16* cache = kind == 1 ? p.k_cache : p.v_cache;
-        *reinterpret_cast<uint4*>(cache + (slot * p.KVH + head) * kD + l * 8) = w;
+    if (ch.live && kind != 2) {
+        __nv_bfloat16* dst = kind == 0 ? p.q + (ch.t * p.H + head) * kD : p.k + (ch.t * p.KVH + head) * kD;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(dst + (q + 4 * i) * 8) = out[i];
     }
+    if (ch.live && kind != 0 && ch.slot >= 0 && ch.slot < p.num_slots) {
+        __nv_bfloat16* cache = (kind == 1 ? p.k_cache : p.v_cache) + (ch.slot * p.KVH + head) * kD;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(cache + (q + 4 * i) * 8) = out[i];
+    }
+}
+
+// The share of block `block` (kThreads threads): rows [block * 64, block * 64 + 64) of the T * (H + 2 KVH) rows, four
+// lanes per row, 64 bytes per lane.
+__device__ __forceinline__ void pre_attention_block(int64_t block, const Params& p) {
+    const int q = threadIdx.x & 3;
+    const Part c = load_part(block * kRowsPerBlock + (threadIdx.x >> 2), q, p);
+    finish_part(c, q, p);
 }
 
 }  // namespace preattn
